@@ -1,0 +1,324 @@
+"""Benchmark of the fused CD-SSM scan (the scan-kernel sweep configuration).
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation
+    python bench.py --impl reference ...                     # the CPU restatement, timed
+
+One step = one pass of the fused scan path over the whole synthetic batch.  At N > 1 the batch
+is split over the ranks (strong scaling, no data-path collective).  Prints ONE JSON line.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {  # the scan-kernel sweep: bf16 q/k/v, fp32 state, seed 2
+    "cfg2_L4096": dict(B=16, H=32, D=128, N=2, C=128, L=4096, seed=2),
+    "cfg2_L16384": dict(B=16, H=32, D=128, N=2, C=128, L=16384, seed=2),
+    "cfg2_L65536": dict(B=16, H=32, D=128, N=2, C=128, L=65536, seed=2),
+    "cfg0": dict(B=2, H=4, D=64, N=2, C=64, L=512, seed=0),
+}
+DEFAULT_WORKLOAD = "cfg2_L65536"
+
+
+def algorithmic_bytes(w, elem=2):
+    """q, k read; v read; the N+5 per-token gate values read; y written (per token-head)."""
+    per_th = (2 * w["D"] + w["N"] + (w["N"] + 5) + w["N"]) * elem
+    return per_th * w["B"] * w["L"] * w["H"]
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ synthetic inputs
+def head_params(w):
+    import torch
+    g = torch.Generator().manual_seed(w["seed"])
+    H, NH = w["H"], w["N"] // 2
+    alpha_raw = -1.0 + 0.5 * torch.randn(NH, H, generator=g)
+    omega = (torch.rand(NH, H, generator=g) * 2 - 1) * math.pi
+    log_dt_scale = 0.5 * torch.randn(H, generator=g)
+    return alpha_raw, omega, log_dt_scale
+
+
+def make_batch_slice(w, b, device, dtype):
+    """Inputs of batch element b, drawn in the configuration's (H,L,.) shapes from a generator
+    seeded by (seed, b), so a shard does not depend on how many GPUs share the batch; then
+    permuted to the operator layout (L,H,.)."""
+    import torch
+    H, L, D, N = w["H"], w["L"], w["D"], w["N"]
+    g = torch.Generator(device=device).manual_seed(w["seed"] * 1000003 + b)
+    rn = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32)
+    q = torch.nn.functional.normalize(rn(H, L, D), dim=-1).transpose(0, 1).to(dtype).contiguous()
+    k = torch.nn.functional.normalize(rn(H, L, D), dim=-1).transpose(0, 1).to(dtype).contiguous()
+    v = rn(H, L, N).transpose(0, 1).to(dtype).contiguous()
+    beta_raw, sel_B, sel_C, sel_dt, r_gate = [rn(H, L).t() for _ in range(5)]
+    alpha_raw, omega, _ = head_params(w)
+    segs = [alpha_raw[j].to(device).expand(L, H) for j in range(N // 2)]
+    segs += [omega[j].to(device).expand(L, H) for j in range(N // 2)]
+    segs += [sel_B, sel_C, sel_dt, beta_raw, r_gate]
+    gate = torch.cat(segs, dim=-1).to(dtype).contiguous()
+    return q, k, v, gate
+
+
+def consts_for(w):
+    eps = 2.0 ** -7
+    thr = math.sqrt(eps)
+    return (math.log(w["L"]), thr, 16.0 * eps, thr / 5.0, 1.0)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")] + [time.time()])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.th.join(timeout=2)
+
+    def summary(self, t0=None, t1=None):
+        rows = [r for r in self.rows if len(r) >= 7 and r[0].isdigit()]
+        if t0 is not None:   # prefer the samples taken while the timed regions ran
+            inside = [r for r in rows if t0 <= r[-1] <= t1 + 0.2]
+            rows = inside or rows
+        self.rows = rows
+        sm = sorted(int(r[0]) for r in rows)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        mx = max(int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit())
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU baseline (oracle port)
+def cpu_sample_workload(w):
+    """A bounded slice of the workload with the same per-token work: one
+    batch element, all heads, at most 16384 positions (about 0.5 M token-heads per step)."""
+    s = dict(w)
+    s["B"] = 1
+    s["L"] = min(w["L"], 16384)
+    return s
+
+
+def run_cpu_oracle(w, steps, warmup):
+    """Time the CPU restatement of the reference path (oracle/cdssm_oracle.c, all-bf16 rounding
+    like the reference) on a bounded sample.  Returns (tokens/s, seconds per step, sample dict)."""
+    import numpy as np
+    import oracle
+    oracle.build()
+    s = cpu_sample_workload(w)
+    inp = oracle.make_inputs(s["B"], s["H"], s["L"], s["D"], N=s["N"], seed=s["seed"], bf16=True,
+                             context_length=w["L"])
+    args = (inp["q"], inp["k"], inp["v"], inp["gate_raw"], inp["log_dt_scale"], inp["rope_freqs"],
+            inp["consts"], s["N"], s["C"])
+    for _ in range(warmup):
+        oracle.scan_reference(*args, round_bf16=oracle.ROUND_REFERENCE)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        y, _ = oracle.scan_reference(*args, round_bf16=oracle.ROUND_REFERENCE)
+    dt = (time.perf_counter() - t0) / steps
+    # tokens/s of the FULL workload's definition (a token = one position across all H heads):
+    # the sample has H_s of H heads, so scale token-heads to tokens of the full head count
+    tok_heads_per_s = s["B"] * s["L"] * s["H"] / dt
+    return tok_heads_per_s / w["H"], dt, s, float(np.abs(y).max())
+
+
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def reference_arm(args, w, rank):
+    if rank != 0:
+        return
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    tps, dt, s, _ = run_cpu_oracle(w, steps, warmup)
+    cores = cpu_threads()
+    sample = (f"B={s['B']} H={s['H']} L={s['L']} of the workload's B={w['B']} H={w['H']} L={w['L']} "
+              f"(same D, N, C); tokens/s = token-heads/s / {w['H']} heads")
+    line = {"impl": "reference", "metric": "scan_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args.workload, w),
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+            "note": "the reference has no CPU implementation (cdssm/ops.py imports its CUDA extension only); "
+                    "this times the C restatement of its kernels with OpenMP over all host threads"}
+    print(json.dumps(line))
+
+
+def workload_config(name, w):
+    return {"workload": f"{name}: fused CD-SSM scan, B={w['B']} H={w['H']} head_dim={w['D']} state_dim={w['N']} "
+                        f"chunk={w['C']} L={w['L']}, bf16 q/k/v/gates, fp32 state, seed {w['seed']}",
+            "l2": "inputs (>= 1 GB per GPU) are larger than the 126 MB L2",
+            "layout": "operator layout (B,L,H,.), rope_freqs = L^(-h/H), constants from context_length = L"}
+
+
+# ------------------------------------------------------------------ the GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (1 = force the CUDA-core kernels)")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, w, rank)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import cdssm_b200
+    from cdssm_b200 import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the scan path has no CPU fallback")
+    cdssm_b200._lib.lib()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    if w["B"] % world:
+        raise SystemExit(f"batch {w['B']} does not split over {world} ranks")
+    Bl = w["B"] // world
+    mine = range(rank * Bl, (rank + 1) * Bl)          # contiguous batch shard, no data-path collective
+    dt = torch.bfloat16
+    parts = [make_batch_slice(w, b, dev, dt) for b in mine]
+    q, k, v, gate = (torch.stack([p[i] for p in parts]) for i in range(4))
+    del parts
+    _, _, lds = head_params(w)
+    lds = lds.to(dev)
+    H, N, C, L, D = w["H"], w["N"], w["C"], w["L"], w["D"]
+    rope = (1.0 / (float(L) ** (torch.arange(H, dtype=torch.float32) / H))).to(dev)
+    consts = consts_for(w)
+    y = torch.empty(Bl, L, H, N, dtype=dt, device=dev)
+
+    def step():
+        return ops.scan_fused(q, k, v, gate, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            step()
+        t_begin = time.time()
+        ms_total = timed(step, args.steps)
+        # end to end: pinned host inputs -> device -> scan -> result back on the host, every step
+        e2e = None
+        if not args.no_e2e:
+            def pinned_copy(t):
+                h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                h.copy_(t)
+                return h
+
+            hq, hk, hv, hg = (pinned_copy(t) for t in (q, k, v, gate))
+            hy = torch.empty(y.shape, dtype=dt, pin_memory=True)
+            dq, dk, dv, dg = (torch.empty_like(t) for t in (q, k, v, gate))
+
+            def e2e_step():
+                dq.copy_(hq, non_blocking=True)
+                dk.copy_(hk, non_blocking=True)
+                dv.copy_(hv, non_blocking=True)
+                dg.copy_(hg, non_blocking=True)
+                out, _ = ops.scan_fused(dq, dk, dv, dg, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
+                hy.copy_(out, non_blocking=True)
+
+            e2e_steps = max(2, min(args.steps, 5))
+            e2e_step()
+            e2e_ms = timed(e2e_step, e2e_steps)
+            h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg)) * world
+            d2h = hy.numel() * hy.element_size() * world
+            e2e = {"value": w["B"] * L / (e2e_ms / e2e_steps / 1e3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                   "ms_per_step": e2e_ms / e2e_steps}
+        t_end = time.time()
+    ms_step = ms_total / args.steps
+    tokens = w["B"] * L
+    if rank == 0:
+        peak, peak_kind = peaks()
+        abytes = algorithmic_bytes(w) / world                       # per GPU per step
+        achieved = abytes / (ms_step / 1e3) / 1e9
+        line = {"metric": "scan_tokens_per_s", "value": tokens / (ms_step / 1e3), "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": workload_config(args.workload, w),
+                "clocks": clocks.summary(t_begin, t_end), "e2e": e2e,
+                "gpu_launches": 3 * args.steps,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                             "kernel": "the whole step (local pass + carry pass + output pass)",
+                             "algorithmic_bytes_per_launch": abytes}}
+        if not args.no_cpu_baseline and world == 1:
+            tps, dt_s, s, _ = run_cpu_oracle(w, 5, 1)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+                                    "sample": f"B={s['B']} H={s['H']} L={s['L']} slice, {dt_s * 1e3:.0f} ms per pass; "
+                                              "C restatement of the reference kernels (the reference has no CPU path)"}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,583 @@
+// Fused CD-SSM scan on CUDA cores (the general path: any even N <= 32, D <= 128, C <= 256,
+// bf16 or fp32 storage).
+//
+// Reference chunk semantics (cdssm/models/ssd.py:56-111 over intra_chunk_scan.cu:100-195,
+// inter_chunk_scan.cu:52-84, exact_correction.cu:89-150), per head and complex pair:
+//   z_t : local state, zero at the start of every chunk, delta-rule step per token;
+//   s_c : carry into chunk c,  s_{c+1} = gamma_c * s_c + z_{C-1}   (decay product only);
+//   r_t : correction, r_0 = s_c, erase+rotate per token, taken BEFORE step t;
+//   y_t = sel_C * ((z_t + r_t) . q_t + shortcut).
+// Nothing of size (B,L,H,N,D) is stored.  Three launches:
+//   local pass  : per (chunk, head, pair) walk z only -> gamma_c and z_{C-1}  (workspace)
+//   carry pass  : per (batch, head, pair, d) serial over chunks -> s_c in place of z_{C-1}
+//   output pass : per (chunk, head, pair) walk z and r together, read out y
+// The local pass re-reads k, v and the gates (about half of the algorithmic bytes); the
+// tensor-core kernel in scan_tc.cu is the single-pass version for the shapes it supports.
+//
+// Thread mapping: eight lanes own one (chunk, head, pair) unit, each lane D/8 contiguous
+// columns of the two state rows, so a k/q row is fetched with 16-byte loads and a dot product
+// costs three shuffles.  The sixteen units of a block are consecutive (head, pair) of one chunk
+// wherever H*N/2 allows, which makes the strided gate and v reads of a block contiguous.
+// The dynamics of a chunk are computed once per unit into shared memory before the walk.
+#include "cdssm_common.cuh"
+
+namespace cdssm {
+
+constexpr int kLanesPerUnit = 8;
+constexpr int kUnitsPerBlock = 16;
+constexpr int kSimtThreads = kLanesPerUnit * kUnitsPerBlock;   // 128
+constexpr int kMaxChunk = 256;
+
+__device__ __forceinline__ float group_sum(float v) {   // sum over the 8 lanes of a unit
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+// Raw (storage-typed) slice of one row: kCols contiguous columns starting at g*kCols.
+template <typename T, int kCols> struct RowSlice;
+template <int kCols> struct RowSlice<__nv_bfloat16, kCols> {
+    uint4 v[kCols / 8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* row, int g, int D, bool vec) {
+        if (vec) {
+            const uint4* p = reinterpret_cast<const uint4*>(row + g * kCols);
+#pragma unroll
+            for (int i = 0; i < kCols / 8; i++) v[i] = __ldg(p + i);
+        } else {
+            unsigned short* s = reinterpret_cast<unsigned short*>(v);
+#pragma unroll
+            for (int i = 0; i < kCols; i++) {
+                const int d = g * kCols + i;
+                s[i] = d < D ? __ldg(reinterpret_cast<const unsigned short*>(row) + d) : (unsigned short)0;
+            }
+        }
+    }
+    __device__ __forceinline__ void get(float* f) const {
+#pragma unroll
+        for (int i = 0; i < kCols / 8; i++) unpack8(v[i], f + 8 * i);
+    }
+};
+template <int kCols> struct RowSlice<float, kCols> {
+    float4 v[kCols / 4];
+    __device__ __forceinline__ void load(const float* row, int g, int D, bool vec) {
+        if (vec) {
+            const float4* p = reinterpret_cast<const float4*>(row + g * kCols);
+#pragma unroll
+            for (int i = 0; i < kCols / 4; i++) v[i] = __ldg(p + i);
+        } else {
+            float* s = reinterpret_cast<float*>(v);
+#pragma unroll
+            for (int i = 0; i < kCols; i++) {
+                const int d = g * kCols + i;
+                s[i] = d < D ? __ldg(row + d) : 0.f;
+            }
+        }
+    }
+    __device__ __forceinline__ void get(float* f) const {
+        const float* s = reinterpret_cast<const float*>(v);
+#pragma unroll
+        for (int i = 0; i < kCols; i++) f[i] = s[i];
+    }
+};
+
+// x * rsqrt(sum x^2 + 1e-6) over the unit's row, rounded like the reference's K_norm/Q_norm
+// store (normalize_kq.cu:72-79).
+template <typename T, int kCols>
+__device__ __forceinline__ void normalise(float* f) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCols; i++) ss += f[i] * f[i];
+    const float inv = rsqrtf(group_sum(ss) + kEps);
+#pragma unroll
+    for (int i = 0; i < kCols; i++) f[i] = IO<T>::rnd(f[i] * inv);
+}
+
+struct ScanArgs {
+    const void *q, *k, *v, *gate_raw;
+    const float *log_dt_scale, *rope_freqs, *h0;
+    void* y;
+    float *final_state, *tail_state;
+    float* ws_gamma;   // (B,NC,H,NP,2)
+    float* ws_state;   // (B,NC,H,NP,2,D): z_{C-1} after the local pass, s_c after the carry pass
+    DynConsts dc;
+    float shortcut_scale;
+    int B, L, H, D, N, C, NC, pos0;
+    long long units;   // B*NC*H*NP
+};
+
+// Shared-memory staging of one chunk's per-token scalars for the 16 units of a block.
+struct ChunkScalars {
+    float *a_re, *a_im, *beta, *v_re, *v_im, *sel_c;   // each [kUnitsPerBlock][C]
+    __device__ ChunkScalars(float* base, int C) {
+        const int n = kUnitsPerBlock * C;
+        a_re = base; a_im = base + n; beta = base + 2 * n; v_re = base + 3 * n;
+        v_im = base + 4 * n; sel_c = base + 5 * n;
+    }
+};
+
+// Dynamics of the unit's chunk: lane g handles tokens g, g+8, ...  (dynamics_fused.cu:64-139
+// and the vp scale of block.py:194-195).  Padded positions (l >= L) get a = k = v = beta = 0
+// like the reference's zero padding (ssd.py:60-67).
+template <typename T>
+__device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& sm, int ul, int g,
+                                               int b, int c, int hd, int j) {
+    const T* gate = static_cast<const T*>(a.gate_raw);
+    const T* vv = static_cast<const T*>(a.v);
+    const int NH = a.N >> 1, H = a.H;
+    const float lds = a.log_dt_scale[hd], freq = a.rope_freqs[hd];
+    for (int t = g; t < a.C; t += kLanesPerUnit) {
+        const int l = c * a.C + t;
+        float ar = 0.f, ai = 0.f, be = 0.f, vr = 0.f, vi = 0.f, sc = 0.f;
+        if (l < a.L) {
+            const long long bl = (long long)b * a.L + l;
+            const T* gr = gate + bl * (long long)((a.N + 5) * H);
+            const T* s5 = gr + a.N * H;
+            const float pos = (float)(l + a.pos0);
+            DynShared ds = dyn_shared(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd),
+                                      IO<T>::ld(s5 + hd), IO<T>::ld(s5 + H + hd),
+                                      IO<T>::ld(s5 + 2 * H + hd), IO<T>::ld(s5 + 3 * H + hd),
+                                      IO<T>::ld(s5 + 4 * H + hd), lds, freq, pos, a.dc);
+            float vp;
+            dyn_pair(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds,
+                     ar, ai, vp);
+            ar = IO<T>::rnd(ar);
+            ai = IO<T>::rnd(ai);
+            vp = IO<T>::rnd(vp);
+            be = IO<T>::rnd(ds.beta);
+            sc = IO<T>::rnd(ds.sel_c);
+            const T* vrow = vv + (bl * H + hd) * a.N + 2 * j;
+            vr = IO<T>::rnd(IO<T>::ld(vrow) * vp);
+            vi = IO<T>::rnd(IO<T>::ld(vrow + 1) * vp);
+        }
+        const int o = ul * a.C + t;
+        sm.a_re[o] = ar; sm.a_im[o] = ai; sm.beta[o] = be;
+        sm.v_re[o] = vr; sm.v_im[o] = vi; sm.sel_c[o] = sc;
+    }
+}
+
+// kOutput = false: local pass (z only).  kOutput = true: output pass (z, r, read-out).
+template <typename T, int kCols, bool kOutput>
+__global__ void __launch_bounds__(kSimtThreads)
+scan_walk_kernel(const ScanArgs a) {
+    extern __shared__ float smem[];
+    ChunkScalars sm(smem, a.C);
+    const int ul = threadIdx.x / kLanesPerUnit;          // unit within the block
+    const int g = threadIdx.x % kLanesPerUnit;           // lane within the unit
+    long long u = (long long)blockIdx.x * kUnitsPerBlock + ul;
+    const bool active = u < a.units;
+    if (!active) u = a.units - 1;                        // keep the lane in the shuffles
+    const int NH = a.N >> 1, D = a.D, C = a.C, H = a.H;
+    const int j = (int)(u % NH);
+    const int hd = (int)((u / NH) % H);
+    const int c = (int)((u / ((long long)NH * H)) % a.NC);
+    const int b = (int)(u / ((long long)NH * H * a.NC));
+    const bool vec = (D == kCols * kLanesPerUnit);       // rows are 16-byte aligned slices
+
+    stage_dynamics<T>(a, sm, ul, g, b, c, hd, j);
+    __syncwarp();
+
+    const int Lc = min(C, a.L - c * C);                  // valid tokens of this chunk
+    const T* kbase = static_cast<const T*>(a.k) + (((long long)b * a.L + (long long)c * C) * H + hd) * D;
+    const T* qbase = static_cast<const T*>(a.q) + (((long long)b * a.L + (long long)c * C) * H + hd) * D;
+    const long long rstride = (long long)H * D;
+
+    float zr[kCols], zi[kCols], rr[kCols], ri[kCols];
+#pragma unroll
+    for (int i = 0; i < kCols; i++) { zr[i] = 0.f; zi[i] = 0.f; rr[i] = 0.f; ri[i] = 0.f; }
+    const long long sidx = ((((long long)b * a.NC + c) * H + hd) * NH + j);
+    if (kOutput) {
+        const float* s = a.ws_state + sidx * 2 * D;
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int d = g * kCols + i;
+            if (d < D) { rr[i] = s[d]; ri[i] = s[D + d]; }
+        }
+    }
+    float cr = 1.f, ci = 0.f;
+
+    RowSlice<T, kCols> kraw, qraw;
+    kraw.load(kbase, g, D, vec);
+    if (kOutput) qraw.load(qbase, g, D, vec);
+    const int so = ul * C;
+    for (int t = 0; t < Lc; t++) {
+        float kk[kCols], qq[kCols];
+        kraw.get(kk);
+        if (kOutput) qraw.get(qq);
+        if (t + 1 < Lc) {
+            kraw.load(kbase + (long long)(t + 1) * rstride, g, D, vec);
+            if (kOutput) qraw.load(qbase + (long long)(t + 1) * rstride, g, D, vec);
+        }
+        normalise<T, kCols>(kk);
+        const float a_re = sm.a_re[so + t], a_im = sm.a_im[so + t], be = sm.beta[so + t];
+        const float vr = sm.v_re[so + t], vi = sm.v_im[so + t];
+        float yr = 0.f, yi = 0.f, qk = 0.f;
+        if (kOutput) {
+            normalise<T, kCols>(qq);
+            // correction is read BEFORE its step (exact_correction.cu:90-94)
+#pragma unroll
+            for (int i = 0; i < kCols; i++) { yr += rr[i] * qq[i]; yi += ri[i] * qq[i]; }
+            float wr = 0.f, wi = 0.f;
+#pragma unroll
+            for (int i = 0; i < kCols; i++) { wr += rr[i] * kk[i]; wi += ri[i] * kk[i]; }
+            wr = be * group_sum(wr);
+            wi = be * group_sum(wi);
+#pragma unroll
+            for (int i = 0; i < kCols; i++) {
+                const float er = rr[i] - wr * kk[i], ei = ri[i] - wi * kk[i];
+                rr[i] = a_re * er - a_im * ei;
+                ri[i] = a_re * ei + a_im * er;
+            }
+        }
+        float ur = 0.f, ui = 0.f;
+#pragma unroll
+        for (int i = 0; i < kCols; i++) { ur += zr[i] * kk[i]; ui += zi[i] * kk[i]; }
+        ur = be * group_sum(ur);
+        ui = be * group_sum(ui);
+        const float ivr = be * vr, ivi = be * vi;
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const float er = zr[i] - ur * kk[i], ei = zi[i] - ui * kk[i];
+            zr[i] = a_re * er - a_im * ei + ivr * kk[i];
+            zi[i] = a_re * ei + a_im * er + ivi * kk[i];
+        }
+        const float ncr = a_re * cr - a_im * ci, nci = a_re * ci + a_im * cr;
+        cr = ncr;
+        ci = nci;
+        if (kOutput) {
+#pragma unroll
+            for (int i = 0; i < kCols; i++) { yr += zr[i] * qq[i]; yi += zi[i] * qq[i]; }
+            yr = group_sum(yr);
+            yi = group_sum(yi);
+            if (a.shortcut_scale != 0.f) {   // block.py:202-208: sum_d shortcut[s,d] q[d] = (q.k)^2 v[s]
+#pragma unroll
+                for (int i = 0; i < kCols; i++) qk += qq[i] * kk[i];
+                qk = group_sum(qk);
+                const float f = a.shortcut_scale * qk * qk;
+                yr += f * vr;
+                yi += f * vi;
+            }
+            if (g == 0) {   // v slots of this step are consumed: reuse them to stage y
+                const float sc = sm.sel_c[so + t];
+                sm.v_re[so + t] = IO<T>::rnd(IO<T>::rnd(yr) * sc);
+                sm.v_im[so + t] = IO<T>::rnd(IO<T>::rnd(yi) * sc);
+            }
+            if (a.tail_state != nullptr && c * C + t == a.L - 1 && active) {
+                float* ts = a.tail_state + (((long long)b * H + hd) * a.N + 2 * j) * D;
+#pragma unroll
+                for (int i = 0; i < kCols; i++) {
+                    const int d = g * kCols + i;
+                    if (d < D) { ts[d] = zr[i] + rr[i]; ts[D + d] = zi[i] + ri[i]; }
+                }
+            }
+        }
+    }
+    if (!kOutput) {
+        if (Lc < C) {   // zero padding wipes the local state and the decay product
+#pragma unroll
+            for (int i = 0; i < kCols; i++) { zr[i] = 0.f; zi[i] = 0.f; }
+            cr = 0.f;
+            ci = 0.f;
+        }
+        if (active) {
+            // the carry pass consumes these as the reference's bf16 cum_A[:, -1] / local_h[:, -1]
+            float* s = a.ws_state + sidx * 2 * D;
+#pragma unroll
+            for (int i = 0; i < kCols; i++) {
+                const int d = g * kCols + i;
+                if (d < D) { s[d] = IO<T>::rnd(zr[i]); s[D + d] = IO<T>::rnd(zi[i]); }
+            }
+            if (g == 0) {
+                a.ws_gamma[sidx * 2] = IO<T>::rnd(cr);
+                a.ws_gamma[sidx * 2 + 1] = IO<T>::rnd(ci);
+            }
+        }
+    } else {
+        __syncwarp();
+        if (active) {
+            T* y = static_cast<T*>(a.y);
+            for (int t = g; t < Lc; t += kLanesPerUnit) {
+                T* o = y + (((long long)b * a.L + c * C + t) * H + hd) * a.N + 2 * j;
+                IO<T>::st(o, sm.v_re[so + t]);
+                IO<T>::st(o + 1, sm.v_im[so + t]);
+            }
+        }
+    }
+}
+
+// Carry pass: s_0 = h0 (or 0); for every chunk: publish s_c, then s <- gamma_c * s + z_{C-1}.
+// One thread per (b, h, pair, d).  Chunks are taken eight at a time so that the loads of a
+// batch are in flight together (the recurrence itself is two FMAs per chunk).
+template <typename T>
+__global__ void __launch_bounds__(128)
+scan_carry_kernel(const ScanArgs a) {
+    const int NH = a.N >> 1, D = a.D, H = a.H, NC = a.NC;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)a.B * H * NH * D) return;
+    const int d = (int)(idx % D);
+    const int j = (int)((idx / D) % NH);
+    const int hd = (int)((idx / ((long long)D * NH)) % H);
+    const int b = (int)(idx / ((long long)D * NH * H));
+    const long long so = (((long long)b * H + hd) * a.N + 2 * j) * D + d;
+    float sr = 0.f, si = 0.f;
+    if (a.h0) { sr = a.h0[so]; si = a.h0[so + D]; }
+    const long long cstride = (long long)H * NH;            // units per chunk index
+    const long long u0 = ((long long)b * NC * H + hd) * NH + j;
+    constexpr int kBatch = 8;
+    for (int c0 = 0; c0 < NC; c0 += kBatch) {
+        float gr[kBatch], gi[kBatch], lr[kBatch], li[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+            if (c0 + i < NC) {
+                const long long u = u0 + (long long)(c0 + i) * cstride;
+                gr[i] = a.ws_gamma[u * 2];
+                gi[i] = a.ws_gamma[u * 2 + 1];
+                lr[i] = a.ws_state[u * 2 * D + d];
+                li[i] = a.ws_state[u * 2 * D + D + d];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+            if (c0 + i < NC) {
+                const long long u = u0 + (long long)(c0 + i) * cstride;
+                a.ws_state[u * 2 * D + d] = IO<T>::rnd(sr);       // chunk_states store
+                a.ws_state[u * 2 * D + D + d] = IO<T>::rnd(si);
+                const float nr = gr[i] * sr - gi[i] * si + lr[i];
+                const float ni = gr[i] * si + gi[i] * sr + li[i];
+                sr = nr;
+                si = ni;
+            }
+        }
+    }
+    if (a.final_state) { a.final_state[so] = sr; a.final_state[so + D] = si; }
+}
+
+template <typename T, int kCols>
+static int launch_simt(const ScanArgs& a, cudaStream_t st) {
+    const size_t smem = (size_t)6 * kUnitsPerBlock * a.C * sizeof(float);
+    if (smem > 48 * 1024) {   // opt in to more than 48 KB of dynamic shared memory (C > 128)
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_walk_kernel<T, kCols, false>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+            return rc;
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_walk_kernel<T, kCols, true>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+            return rc;
+    }
+    const unsigned blocks = (unsigned)((a.units + kUnitsPerBlock - 1) / kUnitsPerBlock);
+    scan_walk_kernel<T, kCols, false><<<blocks, kSimtThreads, smem, st>>>(a);
+    if (int rc = check_launch()) return rc;
+    const long long th = (long long)a.B * a.H * (a.N / 2) * a.D;
+    scan_carry_kernel<T><<<(unsigned)((th + 127) / 128), 128, 0, st>>>(a);
+    if (int rc = check_launch()) return rc;
+    scan_walk_kernel<T, kCols, true><<<blocks, kSimtThreads, smem, st>>>(a);
+    return check_launch();
+}
+
+int scan_fused_simt(const ScanArgs& a, int dtype, cudaStream_t st) {
+    const int cols = (a.D + kLanesPerUnit - 1) / kLanesPerUnit;
+    if (dtype == CDSSM_BF16) {
+        return cols <= 8 ? launch_simt<__nv_bfloat16, 8>(a, st) : launch_simt<__nv_bfloat16, 16>(a, st);
+    }
+    return cols <= 8 ? launch_simt<float, 8>(a, st) : launch_simt<float, 16>(a, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// One-token decode step.  Eight lanes per (batch, head, pair): dynamics for position `pos`,
+// normalise q/k, one delta-rule step on the fp32 state in place, read-out.  One pass over the
+// state (read + write), everything else is a few hundred bytes per head.
+struct DecodeArgs {
+    float* state;
+    const void *q, *k, *v, *gate_raw;
+    const float *log_dt_scale, *rope_freqs;
+    void* y;
+    DynConsts dc;
+    float shortcut_scale;
+    int B, H, D, N, pos;
+    long long units;   // B*H*NP
+};
+
+template <typename T, int kCols>
+__global__ void __launch_bounds__(kSimtThreads)
+decode_step_kernel(const DecodeArgs a) {
+    const int g = threadIdx.x % kLanesPerUnit;
+    long long u = (long long)blockIdx.x * kUnitsPerBlock + threadIdx.x / kLanesPerUnit;
+    const bool active = u < a.units;
+    if (!active) u = a.units - 1;
+    const int NH = a.N >> 1, D = a.D, H = a.H;
+    const int j = (int)(u % NH);
+    const int hd = (int)((u / NH) % H);
+    const long long b = u / ((long long)NH * H);
+    const bool vec = (D == kCols * kLanesPerUnit);
+    const long long bh = b * H + hd;
+
+    RowSlice<T, kCols> kraw, qraw;
+    kraw.load(static_cast<const T*>(a.k) + bh * D, g, D, vec);
+    qraw.load(static_cast<const T*>(a.q) + bh * D, g, D, vec);
+    float* st = a.state + (bh * a.N + 2 * j) * D;
+    float zr[kCols], zi[kCols];
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < kCols / 4; i++) {
+            const float4 x = *reinterpret_cast<const float4*>(st + g * kCols + 4 * i);
+            const float4 w = *reinterpret_cast<const float4*>(st + D + g * kCols + 4 * i);
+            zr[4 * i] = x.x; zr[4 * i + 1] = x.y; zr[4 * i + 2] = x.z; zr[4 * i + 3] = x.w;
+            zi[4 * i] = w.x; zi[4 * i + 1] = w.y; zi[4 * i + 2] = w.z; zi[4 * i + 3] = w.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int d = g * kCols + i;
+            zr[i] = d < D ? st[d] : 0.f;
+            zi[i] = d < D ? st[D + d] : 0.f;
+        }
+    }
+    // dynamics (every lane of the unit computes the same scalars; dynamics_fused.cu:64-139)
+    const T* gr = static_cast<const T*>(a.gate_raw) + b * (long long)((a.N + 5) * H);
+    const T* s5 = gr + a.N * H;
+    const float freq = a.rope_freqs[hd], pos = (float)a.pos;
+    DynShared ds = dyn_shared(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd), IO<T>::ld(s5 + hd),
+                              IO<T>::ld(s5 + H + hd), IO<T>::ld(s5 + 2 * H + hd),
+                              IO<T>::ld(s5 + 3 * H + hd), IO<T>::ld(s5 + 4 * H + hd),
+                              a.log_dt_scale[hd], freq, pos, a.dc);
+    float a_re, a_im, vp;
+    dyn_pair(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds, a_re, a_im, vp);
+    a_re = IO<T>::rnd(a_re);
+    a_im = IO<T>::rnd(a_im);
+    vp = IO<T>::rnd(vp);
+    const float be = IO<T>::rnd(ds.beta), sc = IO<T>::rnd(ds.sel_c);
+    const T* vrow = static_cast<const T*>(a.v) + bh * a.N + 2 * j;
+    const float vr = IO<T>::rnd(IO<T>::ld(vrow) * vp), vi = IO<T>::rnd(IO<T>::ld(vrow + 1) * vp);
+
+    float kk[kCols], qq[kCols];
+    kraw.get(kk);
+    qraw.get(qq);
+    normalise<T, kCols>(kk);
+    normalise<T, kCols>(qq);
+    float ur = 0.f, ui = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCols; i++) { ur += zr[i] * kk[i]; ui += zi[i] * kk[i]; }
+    ur = be * group_sum(ur);
+    ui = be * group_sum(ui);
+    const float ivr = be * vr, ivi = be * vi;
+    float yr = 0.f, yi = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCols; i++) {
+        const float er = zr[i] - ur * kk[i], ei = zi[i] - ui * kk[i];
+        zr[i] = a_re * er - a_im * ei + ivr * kk[i];
+        zi[i] = a_re * ei + a_im * er + ivi * kk[i];
+        yr += zr[i] * qq[i];
+        yi += zi[i] * qq[i];
+    }
+    yr = group_sum(yr);
+    yi = group_sum(yi);
+    if (a.shortcut_scale != 0.f) {
+        float qk = 0.f;
+#pragma unroll
+        for (int i = 0; i < kCols; i++) qk += qq[i] * kk[i];
+        qk = group_sum(qk);
+        const float f = a.shortcut_scale * qk * qk;
+        yr += f * vr;
+        yi += f * vi;
+    }
+    if (!active) return;
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < kCols / 4; i++) {
+            *reinterpret_cast<float4*>(st + g * kCols + 4 * i) =
+                make_float4(zr[4 * i], zr[4 * i + 1], zr[4 * i + 2], zr[4 * i + 3]);
+            *reinterpret_cast<float4*>(st + D + g * kCols + 4 * i) =
+                make_float4(zi[4 * i], zi[4 * i + 1], zi[4 * i + 2], zi[4 * i + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int d = g * kCols + i;
+            if (d < D) { st[d] = zr[i]; st[D + d] = zi[i]; }
+        }
+    }
+    if (g == 0) {
+        T* o = static_cast<T*>(a.y) + bh * a.N + 2 * j;
+        IO<T>::st(o, IO<T>::rnd(yr) * sc);
+        IO<T>::st(o + 1, IO<T>::rnd(yi) * sc);
+    }
+}
+
+template <typename T, int kCols>
+static int launch_decode(const DecodeArgs& a, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((a.units + kUnitsPerBlock - 1) / kUnitsPerBlock);
+    decode_step_kernel<T, kCols><<<blocks, kSimtThreads, 0, st>>>(a);
+    return check_launch();
+}
+
+}  // namespace cdssm
+
+using namespace cdssm;
+
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+extern "C" size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C) {
+    if (B <= 0 || L <= 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1) || C <= 0) return 0;
+    const size_t NC = ((size_t)L + C - 1) / C;
+    const size_t units = (size_t)B * NC * H * (N / 2);
+    return align256(units * 2 * sizeof(float)) + align256(units * 2 * D * sizeof(float)) + 256;
+}
+
+extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void* v,
+                                         const void* gate_raw, const float* log_dt_scale,
+                                         const float* rope_freqs, const float* h0, void* y,
+                                         float* final_state, float* tail_state, void* workspace,
+                                         size_t workspace_bytes, float gating_c,
+                                         float omega_thresh, float adt_delta, float adt_smoothness,
+                                         float adt_eps, float shortcut_scale, int B, int L, int H,
+                                         int D, int N, int C, int pos0, int dtype, int flags,
+                                         void* stream) {
+    (void)flags;
+    if (!q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y) return CDSSM_ERR_BAD_ARG;
+    if (B < 0 || L < 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1) || C <= 0) return CDSSM_ERR_BAD_ARG;
+    if (dtype != CDSSM_BF16 && dtype != CDSSM_F32) return CDSSM_ERR_BAD_ARG;
+    if (((uintptr_t)q | (uintptr_t)k) & 15) return CDSSM_ERR_BAD_ARG;   // 16-byte row loads
+    if (N > kMaxStateDim || D > kMaxHeadDim || C > kMaxChunk) return CDSSM_ERR_UNSUPPORTED;
+    if (B == 0 || L == 0) return CDSSM_OK;
+    const size_t need = cdssm_b200_scan_fused_workspace_bytes(B, L, H, D, N, C);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return CDSSM_ERR_WORKSPACE;
+    ScanArgs a;
+    a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
+    a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.h0 = h0;
+    a.y = y; a.final_state = final_state; a.tail_state = tail_state;
+    a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
+    a.shortcut_scale = shortcut_scale;
+    a.B = B; a.L = L; a.H = H; a.D = D; a.N = N; a.C = C; a.pos0 = pos0;
+    a.NC = (L + C - 1) / C;
+    a.units = (long long)B * a.NC * H * (N / 2);
+    a.ws_gamma = static_cast<float*>(workspace);
+    a.ws_state = reinterpret_cast<float*>(static_cast<char*>(workspace) +
+                                          align256((size_t)a.units * 2 * sizeof(float)));
+    return scan_fused_simt(a, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k, const void* v,
+                                      const void* gate_raw, const float* log_dt_scale,
+                                      const float* rope_freqs, void* y, float gating_c,
+                                      float omega_thresh, float adt_delta, float adt_smoothness,
+                                      float adt_eps, float shortcut_scale, int B, int H, int D,
+                                      int N, int pos, int dtype, void* stream) {
+    if (!state || !q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y)
+        return CDSSM_ERR_BAD_ARG;
+    if (B < 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1)) return CDSSM_ERR_BAD_ARG;
+    if (dtype != CDSSM_BF16 && dtype != CDSSM_F32) return CDSSM_ERR_BAD_ARG;
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)state) & 15) return CDSSM_ERR_BAD_ARG;
+    if (N > kMaxStateDim || D > kMaxHeadDim) return CDSSM_ERR_UNSUPPORTED;
+    if (B == 0) return CDSSM_OK;
+    DecodeArgs a;
+    a.state = state; a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
+    a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.y = y;
+    a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
+    a.shortcut_scale = shortcut_scale;
+    a.B = B; a.H = H; a.D = D; a.N = N; a.pos = pos;
+    a.units = (long long)B * H * (N / 2);
+    const int cols = (D + kLanesPerUnit - 1) / kLanesPerUnit;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == CDSSM_BF16)
+        return cols <= 8 ? launch_decode<__nv_bfloat16, 8>(a, st) : launch_decode<__nv_bfloat16, 16>(a, st);
+    return cols <= 8 ? launch_decode<float, 8>(a, st) : launch_decode<float, 16>(a, st);
+}

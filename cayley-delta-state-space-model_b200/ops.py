@@ -1,0 +1,298 @@
+"""Operator API of the CD-SSM scan path on B200.
+
+Level 1 mirrors the reference's cdssm/ops.py: the same six ``torch.autograd.Function``
+classes, positional signatures, tensor layouts and dtypes (cdssm/ops.py:13-195), so
+cdssm/models/{block,ssd,modules}.py can import this module in its place.  Forward only:
+``backward`` raises NotImplementedError.
+
+Level 2 is the fused path: :func:`scan_fused` (dynamics + normalisation + vp scale + chunked
+scan + read-out in one call) and :func:`decode_step`.
+
+Every function launches hand-written sm_100a kernels through the C ABI of
+libcdssm_b200.so on the current CUDA stream.  There is no CPU, eager-PyTorch or Triton
+fallback: tensors must be CUDA tensors and the library must be built.
+"""
+import torch
+from torch import Tensor
+from torch.autograd import Function
+
+from . import _lib
+from ._lib import CdssmError, check
+
+__all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
+           "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
+           "scan_fused_workspace_bytes", "CdssmError"]
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+
+def _dtype_code(t: Tensor) -> int:
+    if t.dtype not in _DT:
+        raise CdssmError(f"unsupported dtype {t.dtype}: use bfloat16 (the reference's type) or float32")
+    return _DT[t.dtype]
+
+
+def _prep(t: Tensor, dtype=None, name="tensor") -> Tensor:
+    """The reference launchers call .contiguous() and never check dtypes (e.g.
+    intra_chunk_scan.cu:573-603); here a wrong device or dtype is an error, not garbage."""
+    if not t.is_cuda:
+        raise CdssmError(f"{name} must be a CUDA tensor (no CPU fallback exists)")
+    if dtype is not None and t.dtype != dtype:
+        raise CdssmError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    return t.contiguous()
+
+
+def _f32(t: Tensor, name) -> Tensor:
+    """Per-head fp32 vectors; a bf16 buffer (a model cast with .bfloat16()) is converted."""
+    if not t.is_cuda:
+        raise CdssmError(f"{name} must be a CUDA tensor")
+    return t.detach().to(torch.float32).contiguous()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _no_backward(*_):
+    raise NotImplementedError("this build implements the forward (prefill/decode) path only")
+
+
+class CUDAConv1dSiLUOp(Function):
+    """Causal depthwise conv (kernel 4) + bias + SiLU; cdssm/ops.py:13-28."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Tensor) -> Tensor:
+        x = _prep(x, name="x")
+        if weight.shape[-1] != 4:
+            raise CdssmError("Only kernel_size=4 is supported")   # conv1d_silu.cu:241
+        B, L, Dm = x.shape
+        w = _prep(weight.detach().to(x.dtype), name="weight").reshape(Dm, 4)
+        b = _prep(bias.detach().to(x.dtype), name="bias")
+        out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            check(_lib.lib().cdssm_b200_conv1d_silu_fwd(_p(x), _p(w), _p(b), _p(out), B, L, Dm,
+                                                        _dtype_code(x), _stream()), "conv1d_silu_fwd")
+        return out
+
+    backward = staticmethod(_no_backward)
+
+
+class DynamicsFusedFn(Function):
+    """gate_raw -> A_bar, vp_scale, beta, sel_C_gate; cdssm/ops.py:31-81."""
+
+    @staticmethod
+    def forward(ctx, gate_raw: Tensor, log_dt_scale: Tensor, rope_freqs: Tensor, gating_c: float,
+                omega_thresh: float, adt_delta: float, adt_smoothness: float, adt_eps: float,
+                n_heads: int, state_dim: int):
+        g = _prep(gate_raw, name="gate_raw")
+        B, L, GH = g.shape
+        H, N = int(n_heads), int(state_dim)
+        if GH != (N + 5) * H:
+            raise CdssmError(f"gate_raw last dim {GH} != (state_dim+5)*n_heads = {(N + 5) * H}")
+        lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
+        o = dict(dtype=g.dtype, device=g.device)
+        A = torch.empty(B, L, H, N, **o)
+        vp = torch.empty(B, L, H, N // 2, **o)
+        beta = torch.empty(B, L, H, **o)
+        selc = torch.empty(B, L, H, **o)
+        with torch.cuda.device(g.device):
+            check(_lib.lib().cdssm_b200_dynamics_fwd(
+                _p(g), _p(lds), _p(rf), _p(A), _p(vp), _p(beta), _p(selc), gating_c, omega_thresh,
+                adt_delta, adt_smoothness, adt_eps, B, L, H, N, 0, _dtype_code(g), _stream()),
+                "dynamics_fwd")
+        return A, vp, beta, selc
+
+    backward = staticmethod(_no_backward)
+
+
+class NormalizeKQFn(Function):
+    """L2-normalise K and Q over the last dim; cdssm/ops.py:84-97."""
+
+    @staticmethod
+    def forward(ctx, K: Tensor, Q: Tensor):
+        K = _prep(K, name="K")
+        Q = _prep(Q, dtype=K.dtype, name="Q")
+        if K.shape != Q.shape:
+            raise CdssmError("K and Q must have the same shape")
+        D = K.shape[-1]
+        Ko, Qo = torch.empty_like(K), torch.empty_like(Q)
+        with torch.cuda.device(K.device):
+            check(_lib.lib().cdssm_b200_normalize_kq_fwd(_p(K), _p(Q), _p(Ko), _p(Qo),
+                                                         K.numel() // D, D, _dtype_code(K), _stream()),
+                  "normalize_kq_fwd")
+        return Ko, Qo
+
+    backward = staticmethod(_no_backward)
+
+
+class IntraChunkScanFn(Function):
+    """Chunk-local delta-rule scan from a zero state; cdssm/ops.py:100-135."""
+
+    @staticmethod
+    def forward(ctx, A_flat: Tensor, K_flat: Tensor, V_flat: Tensor, beta_flat: Tensor, state_dim: int):
+        K = _prep(K_flat, name="K_flat")
+        A = _prep(A_flat, dtype=K.dtype, name="A_flat")
+        V = _prep(V_flat, dtype=K.dtype, name="V_flat")
+        be = _prep(beta_flat, dtype=K.dtype, name="beta_flat")
+        BNC, C, H, D = K.shape
+        N = int(state_dim)
+        local_h = torch.empty(BNC, C, H, N, D, dtype=K.dtype, device=K.device)
+        cum_A = torch.empty(BNC, C, H, N, dtype=K.dtype, device=K.device)
+        with torch.cuda.device(K.device):
+            check(_lib.lib().cdssm_b200_intra_chunk_scan_fwd(
+                _p(A), _p(K), _p(V), _p(be), _p(local_h), _p(cum_A), BNC, C, H, D, N,
+                _dtype_code(K), _stream()), "intra_chunk_scan_fwd")
+        return local_h, cum_A
+
+    backward = staticmethod(_no_backward)
+
+
+class InterChunkScanFn(Function):
+    """Carry recurrence across chunks; cdssm/ops.py:138-163."""
+
+    @staticmethod
+    def forward(ctx, total_A: Tensor, final_local_h: Tensor, state_dim: int) -> Tensor:
+        f = _prep(final_local_h, name="final_local_h")
+        a = _prep(total_A, dtype=f.dtype, name="total_A")
+        B, NC, H, N, D = f.shape
+        out = torch.empty_like(f)
+        with torch.cuda.device(f.device):
+            check(_lib.lib().cdssm_b200_inter_chunk_scan_fwd(_p(a), _p(f), _p(out), B, NC, H, D,
+                                                             int(state_dim), _dtype_code(f), _stream()),
+                  "inter_chunk_scan_fwd")
+        return out
+
+    backward = staticmethod(_no_backward)
+
+
+class ExactCorrectionFn(Function):
+    """Propagate chunk carries through erase+rotate; cdssm/ops.py:166-195."""
+
+    @staticmethod
+    def forward(ctx, A_chunk: Tensor, K_chunk: Tensor, beta_chunk: Tensor, chunk_states: Tensor,
+                state_dim: int) -> Tensor:
+        K = _prep(K_chunk, name="K_chunk")
+        A = _prep(A_chunk, dtype=K.dtype, name="A_chunk")
+        be = _prep(beta_chunk, dtype=K.dtype, name="beta_chunk")
+        cs = _prep(chunk_states, dtype=K.dtype, name="chunk_states")
+        B, NC, C, H, D = K.shape
+        N = int(state_dim)
+        out = torch.empty(B, NC, C, H, N, D, dtype=K.dtype, device=K.device)
+        with torch.cuda.device(K.device):
+            check(_lib.lib().cdssm_b200_exact_correction_fwd(
+                _p(A), _p(K), _p(be), _p(cs), _p(out), B, NC, C, H, D, N, _dtype_code(K), _stream()),
+                "exact_correction_fwd")
+        return out
+
+    backward = staticmethod(_no_backward)
+
+
+# ------------------------------------------------------------------------------------------
+# Level 2: the fused path
+# ------------------------------------------------------------------------------------------
+FORCE_SIMT = 1
+
+_workspaces = {}
+
+
+def scan_fused_workspace_bytes(B, L, H, D, N, C) -> int:
+    return int(_lib.lib().cdssm_b200_scan_fused_workspace_bytes(B, L, H, D, N, C))
+
+
+def _workspace(device, nbytes):
+    """One grow-only scratch buffer per (device, stream); the library itself allocates nothing."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    off = (-buf.data_ptr()) % 256
+    return buf.data_ptr() + off, buf.numel() - off
+
+
+def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor,
+               rope_freqs: Tensor, gating_c: float, omega_thresh: float, adt_delta: float,
+               adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int,
+               chunk_size: int, h0: Tensor = None, *, shortcut_scale: float = 0.0, pos0: int = 0,
+               return_tail_state: bool = False, flags: int = 0, out: Tensor = None):
+    """The scan path of one CD-SSM block in a single call.
+
+    Equals, in the reference (cdssm/models/block.py:181-211): DynamicsFusedFn -> NormalizeKQFn
+    -> V * vp_scale -> SSDChunkwiseScan (cdssm/models/ssd.py:39-111) -> shortcut -> einsum
+    read-out -> sel_C gate, with the reference's chunk semantics, but without ever storing a
+    (B,L,H,N,D) tensor.
+
+    q, k: (B,L,H,D) un-normalised; v: (B,L,H,N) before the vp scale; gate_raw: (B,L,(N+5)H);
+    log_dt_scale, rope_freqs: (H).  h0: optional (B,H,N,D) float32 carry into the first chunk.
+    Returns (y (B,L,H,N), final_state (B,H,N,D) float32[, tail_state]); final_state is the carry
+    after the last chunk (feed it as h0 of the next chunk-aligned segment together with pos0);
+    tail_state is the recurrent state after the last token (what decode_step continues from).
+    """
+    q = _prep(q, name="q")
+    k = _prep(k, dtype=q.dtype, name="k")
+    v = _prep(v, dtype=q.dtype, name="v")
+    g = _prep(gate_raw, dtype=q.dtype, name="gate_raw")
+    B, L, H, D = q.shape
+    N, C = int(state_dim), int(chunk_size)
+    if H != int(n_heads) or k.shape != q.shape or tuple(v.shape) != (B, L, H, N) or \
+            tuple(g.shape) != (B, L, (N + 5) * H):
+        raise CdssmError("scan_fused: inconsistent shapes")
+    lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
+    if h0 is not None:
+        h0 = _prep(h0, dtype=torch.float32, name="h0")
+        if tuple(h0.shape) != (B, H, N, D):
+            raise CdssmError("h0 must be (B,H,N,D)")
+    dev = q.device
+    y = out if out is not None else torch.empty(B, L, H, N, dtype=q.dtype, device=dev)
+    if out is not None and (tuple(out.shape) != (B, L, H, N) or out.dtype != q.dtype or not out.is_contiguous()):
+        raise CdssmError("out must be a contiguous (B,L,H,N) tensor of the input dtype")
+    final = torch.empty(B, H, N, D, dtype=torch.float32, device=dev)
+    tail = torch.empty(B, H, N, D, dtype=torch.float32, device=dev) if return_tail_state else None
+    if B * L == 0:   # nothing to scan: the carry passes through
+        final.zero_() if h0 is None else final.copy_(h0)
+        if tail is not None:
+            tail.copy_(final)
+        return (y, final, tail) if return_tail_state else (y, final)
+    with torch.cuda.device(dev):
+        ws_ptr, ws_bytes = _workspace(dev, scan_fused_workspace_bytes(B, L, H, D, N, C))
+        check(_lib.lib().cdssm_b200_scan_fused_fwd(
+            _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(y), _p(final), _p(tail), ws_ptr,
+            ws_bytes, gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale,
+            B, L, H, D, N, C, int(pos0), _dtype_code(q), int(flags), _stream()), "scan_fused_fwd")
+    return (y, final, tail) if return_tail_state else (y, final)
+
+
+def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor,
+                log_dt_scale: Tensor, rope_freqs: Tensor, gating_c: float, omega_thresh: float,
+                adt_delta: float, adt_smoothness: float, adt_eps: float, n_heads: int,
+                state_dim: int, pos: int, *, shortcut_scale: float = 0.0, out: Tensor = None) -> Tensor:
+    """One recurrent step for every sequence of a batch; ``state`` (B,H,N,D) float32 is updated
+    in place.  q, k: (B,H,D); v: (B,H,N); gate_raw: (B,(N+5)H); returns y (B,H,N).
+
+    The reference has no such step (cdssm/inference/predict.py:53-67 re-runs the full forward
+    for every new token); the update is one iteration of intra_chunk_scan.cu:117-167 with the
+    gates of dynamics_fused.cu:64-139 at position ``pos``.
+    """
+    q = _prep(q, name="q")
+    k = _prep(k, dtype=q.dtype, name="k")
+    v = _prep(v, dtype=q.dtype, name="v")
+    g = _prep(gate_raw, dtype=q.dtype, name="gate_raw")
+    if not state.is_cuda or state.dtype != torch.float32 or not state.is_contiguous():
+        raise CdssmError("state must be a contiguous float32 CUDA tensor (B,H,N,D)")
+    B, H, D = q.shape
+    N = int(state_dim)
+    if H != int(n_heads) or tuple(state.shape) != (B, H, N, D) or tuple(v.shape) != (B, H, N) or \
+            tuple(g.shape) != (B, (N + 5) * H):
+        raise CdssmError("decode_step: inconsistent shapes")
+    lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
+    y = out if out is not None else torch.empty(B, H, N, dtype=q.dtype, device=q.device)
+    with torch.cuda.device(q.device):
+        check(_lib.lib().cdssm_b200_decode_step(
+            _p(state), _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh,
+            adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, int(pos), _dtype_code(q),
+            _stream()), "decode_step")
+    return y

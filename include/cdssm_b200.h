@@ -1,0 +1,139 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the CD-SSM scan path.
+ *
+ * Plain pointers and sizes only: every pointer is a CUDA device pointer unless its comment
+ * says "host"; `stream` is a cudaStream_t passed as void*.  Calls enqueue work on `stream`
+ * and return without synchronising.  Return value: CDSSM_OK or a negative CDSSM_ERR_* code;
+ * nothing throws.  The library allocates no device memory: outputs and workspaces are the
+ * caller's.  `dtype` selects the storage type of every activation tensor of the call:
+ * CDSSM_BF16 (the only type the reference supports) or CDSSM_F32 (same arithmetic with no
+ * intermediate rounding).
+ *
+ * Layouts are the reference operator layouts (cdssm/ops.py docstrings): sequence-major,
+ * head-minor.  "Replaces" lines cite the reference entry point each function stands in for.
+ */
+#ifndef CDSSM_B200_H
+#define CDSSM_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CDSSM_API __attribute__((visibility("default")))
+#else
+#define CDSSM_API
+#endif
+
+#define CDSSM_OK 0
+#define CDSSM_ERR_BAD_ARG (-1)      /* null pointer, non-positive size, odd N, misalignment */
+#define CDSSM_ERR_UNSUPPORTED (-2)  /* size outside the supported range (N > 32, D > 128, ...) */
+#define CDSSM_ERR_WORKSPACE (-3)    /* workspace missing or too small */
+#define CDSSM_ERR_CUDA (-4)         /* a CUDA runtime call failed; see cdssm_b200_last_cuda_error */
+#define CDSSM_ERR_TIMEOUT (-5)      /* a bounded device-side wait ran out (status word set) */
+
+#define CDSSM_BF16 0
+#define CDSSM_F32 1
+
+/* Library version (major*10000 + minor*100 + patch) and the CUDA error of the last failed call
+ * on this host thread (0 if none). */
+CDSSM_API int cdssm_b200_version(void);
+CDSSM_API int cdssm_b200_last_cuda_error(void);
+
+/* Fused dynamics: gate_raw (B,L,(N+5)*H) -> A_bar (B,L,H,N), vp_scale (B,L,H,N/2),
+ * beta (B,L,H), sel_C (B,L,H).  log_dt_scale, rope_freqs: (H) float32.  pos0 is added to the
+ * token index (the reference always uses 0).
+ * Replaces dynamics_fused_fwd_cuda, cdssm/csrc/kernels/dynamics_fused.cu:392-440
+ * (bound at cdssm/csrc/binding.cpp:130-202, called from cdssm/ops.py:53). */
+CDSSM_API int cdssm_b200_dynamics_fwd(const void* gate_raw, const float* log_dt_scale,
+                            const float* rope_freqs, void* A_bar, void* vp_scale, void* beta,
+                            void* sel_C, float gating_c, float omega_thresh, float adt_delta,
+                            float adt_smoothness, float adt_eps, int B, int L, int H, int N,
+                            int pos0, int dtype, void* stream);
+
+/* L2 normalisation of K and Q rows, x * rsqrt(sum x^2 + 1e-6); rows = B*L*H, any D >= 1.
+ * Replaces normalize_kq_fwd_cuda, cdssm/csrc/kernels/normalize_kq.cu:168-204 (cdssm/ops.py:89). */
+CDSSM_API int cdssm_b200_normalize_kq_fwd(const void* K, const void* Q, void* K_out, void* Q_out,
+                                int64_t rows, int D, int dtype, void* stream);
+
+/* Intra-chunk delta-rule scan from a zero state.  A (BNC,C,H,N), K (BNC,C,H,D), V (BNC,C,H,N),
+ * beta (BNC,C,H) -> local_h (BNC,C,H,N,D), cum_A (BNC,C,H,N).
+ * Replaces intra_chunk_scan_fwd_cuda, cdssm/csrc/kernels/intra_chunk_scan.cu:560-609
+ * (cdssm/ops.py:116). */
+CDSSM_API int cdssm_b200_intra_chunk_scan_fwd(const void* A, const void* K, const void* V, const void* beta,
+                                    void* local_h, void* cum_A, int BNC, int C, int H, int D,
+                                    int N, int dtype, void* stream);
+
+/* Inter-chunk carry.  total_A (B,NC,H,N), final_local_h (B,NC,H,N,D) -> chunk_states
+ * (B,NC,H,N,D): the carry BEFORE each chunk, s <- total_A (*) s + final_local_h, from s = 0.
+ * Replaces inter_chunk_scan_fwd_cuda, cdssm/csrc/kernels/inter_chunk_scan.cu:201-234
+ * (cdssm/ops.py:152). */
+CDSSM_API int cdssm_b200_inter_chunk_scan_fwd(const void* total_A, const void* final_local_h,
+                                    void* chunk_states, int B, int NC, int H, int D, int N,
+                                    int dtype, void* stream);
+
+/* Correction pass: propagate each chunk's carry through erase+rotate, storing the state BEFORE
+ * each step.  A (B,NC,C,H,N), K (B,NC,C,H,D), beta (B,NC,C,H), chunk_states (B,NC,H,N,D)
+ * -> corrections (B,NC,C,H,N,D).
+ * Replaces exact_correction_fwd_cuda, cdssm/csrc/kernels/exact_correction.cu:390-438
+ * (cdssm/ops.py:181). */
+CDSSM_API int cdssm_b200_exact_correction_fwd(const void* A, const void* K, const void* beta,
+                                    const void* chunk_states, void* corrections, int B, int NC,
+                                    int C, int H, int D, int N, int dtype, void* stream);
+
+/* Causal depthwise 4-tap convolution + bias + SiLU.  x,out (B,L,Dm); weight (Dm,4); bias (Dm).
+ * Replaces conv1d_silu_fwd_cuda, cdssm/csrc/kernels/conv1d_silu.cu:223-274 (cdssm/ops.py:18). */
+CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, const void* bias, void* out,
+                               int B, int L, int Dm, int dtype, void* stream);
+
+/* ---- the fused path -------------------------------------------------------------------- */
+
+/* Flags of cdssm_b200_scan_fused_fwd. */
+#define CDSSM_SCAN_DEFAULT 0
+#define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels even where the tensor-core one applies */
+
+/* Bytes of workspace cdssm_b200_scan_fused_fwd needs for these sizes (0 on bad sizes). */
+CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C);
+
+/* The whole scan path in one call, nothing of size (B,L,H,N,D) ever stored:
+ * dynamics -> L2-normalised q/k -> vp-scaled v -> chunked delta-rule scan in the reference's
+ * chunk semantics (local scan from zero per chunk of C tokens, decay-only carry between chunks,
+ * correction taken before each step) -> shortcut -> read-out with q -> sel_C gate.
+ *   q,k (B,L,H,D) un-normalised; v (B,L,H,N) before the vp scale; gate_raw (B,L,(N+5)*H);
+ *   h0 (B,H,N,D) float32 or NULL: carry into the first chunk;
+ *   y (B,L,H,N); final_state (B,H,N,D) float32 or NULL: carry after the last chunk;
+ *   tail_state (B,H,N,D) float32 or NULL: the recurrent state after token L-1 (what the
+ *   one-token decode step continues from);
+ *   workspace: at least cdssm_b200_scan_fused_workspace_bytes bytes, 256-byte aligned.
+ * With h0 = NULL and shortcut handled as in cdssm/models/block.py:202-211 this equals
+ * DynamicsFusedFn + NormalizeKQFn + SSDChunkwiseScan + the read-out of the reference block.
+ * Replaces the call chain cdssm/models/block.py:181-211 -> cdssm/models/ssd.py:39-111 ->
+ * cdssm/ops.py:53,89,116,152,181. */
+CDSSM_API int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void* v, const void* gate_raw,
+                              const float* log_dt_scale, const float* rope_freqs, const float* h0,
+                              void* y, float* final_state, float* tail_state, void* workspace,
+                              size_t workspace_bytes, float gating_c, float omega_thresh,
+                              float adt_delta, float adt_smoothness, float adt_eps,
+                              float shortcut_scale, int B, int L, int H, int D, int N, int C,
+                              int pos0, int dtype, int flags, void* stream);
+
+/* One-token recurrent decode step for a batch of sequences: dynamics for position `pos`,
+ * normalise q/k, state <- a (*) (state - beta (state k) k^T) + beta v k^T, y = sel_C * (state q
+ * + shortcut).  state (B,H,N,D) float32 is updated in place; q,k (B,H,D); v (B,H,N);
+ * gate_raw (B,(N+5)*H); y (B,H,N).
+ * The reference has no decode step (cdssm/inference/predict.py:53-67 re-runs the whole
+ * forward per token); the formula is one iteration of
+ * cdssm/csrc/kernels/intra_chunk_scan.cu:117-167 with the gates of dynamics_fused.cu:64-139. */
+CDSSM_API int cdssm_b200_decode_step(float* state, const void* q, const void* k, const void* v,
+                           const void* gate_raw, const float* log_dt_scale,
+                           const float* rope_freqs, void* y, float gating_c, float omega_thresh,
+                           float adt_delta, float adt_smoothness, float adt_eps,
+                           float shortcut_scale, int B, int H, int D, int N, int pos, int dtype,
+                           void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CDSSM_B200_H */

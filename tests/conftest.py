@@ -1,0 +1,29 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def orc():
+    import oracle
+    oracle.build()
+    return oracle
+
+
+@pytest.fixture(scope="session")
+def ops():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import cdssm_b200
+    cdssm_b200._lib.lib()          # raises if the library is not built: no silent fallback
+    return cdssm_b200.ops

@@ -1,0 +1,52 @@
+"""Our kernels against the reference's OWN kernels (compiled unmodified for sm_100 into
+oracle/_ref/ by oracle/build_ref.py), on the same bf16 inputs, on the GPU."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from util import BF16_TOL, const_args, rel_err, to_np
+
+pytestmark = pytest.mark.gpu
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from oracle.build_ref import load_ref
+    mod = load_ref()
+    if mod is None:
+        pytest.skip("reference extension not built (oracle/build_ref.py)")
+    return mod
+
+
+def _t(a):
+    from golden.golden_cases import unbits
+    return torch.from_numpy(unbits(a)).cuda().bfloat16()
+
+
+@pytest.mark.parametrize("case", ["d64_pad", "d64_n4_shortcut", "d128"])
+def test_against_reference_kernels(ops, orc, ref, case):
+    from golden.golden_cases import CASES, run_reference, unbits
+    c = CASES[case]
+    g = run_reference(ref, c, orc)
+    B, H, L, D, N, C = (int(x) for x in g["sizes"])
+    consts = tuple(float(x) for x in g["consts"])
+    lds, rf = torch.from_numpy(g["log_dt_scale"]).cuda(), torch.from_numpy(g["rope_freqs"]).cuda()
+    q, k, v, gate = _t(g["q"]), _t(g["k"]), _t(g["v"]), _t(g["gate_raw"])
+    # operator level: same inputs, same rounding points -> bf16-ulp agreement
+    A, vp, beta, selc = ops.DynamicsFusedFn.apply(gate, lds, rf, *consts, H, N)
+    for got, name in ((A, "A_bar"), (vp, "vp"), (beta, "beta"), (selc, "sel_C")):
+        want = unbits(g[name])
+        assert np.mean(to_np(got) == want) > 0.99, name
+        assert rel_err(to_np(got), want) <= 2.0 ** -7, name
+    kn, qn = ops.NormalizeKQFn.apply(k, q)
+    assert rel_err(to_np(kn), unbits(g["k_norm"])) <= 2.0 ** -7
+    assert rel_err(to_np(qn), unbits(g["q_norm"])) <= 2.0 ** -7
+    cs = ops.InterChunkScanFn.apply(_t(g["cum_A"])[:, :, -1], _t(g["local_h_last"]), N)
+    assert rel_err(to_np(cs), unbits(g["chunk_states"])) <= 2.0 ** -7
+    # the fused path against the reference pipeline's final output
+    y, _ = ops.scan_fused(q, k, v, gate, lds, rf, *consts, H, N, C, shortcut_scale=float(g["shortcut"]))
+    assert rel_err(to_np(y), unbits(g["y"])) <= BF16_TOL
