@@ -6,7 +6,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_NAME = "libcdssm_b200.so"
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--use_fast_math",
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 
@@ -46,7 +46,7 @@ def build(force=False, verbose=False):
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
     out = lib_path()
     if force or procs or _stale(out, objs):
-        cmd = [nvcc, "-shared", "-o", out] + objs + ["-lcudart", "-lcuda"]
+        cmd = [nvcc, "-shared", "-o", out] + objs + ["-lcudart"]
         if verbose:
             print(" ".join(cmd))
         subprocess.check_call(cmd)

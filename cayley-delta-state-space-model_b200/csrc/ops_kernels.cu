@@ -33,13 +33,13 @@ dynamics_fwd_kernel(const T* __restrict__ gate_raw, const float* __restrict__ lo
     const T* sc = g + N * H;
     const float freq = rope_freqs[h];
     const float pos = (float)(l + pos0);
-    DynShared s = dyn_shared(IO<T>::ld(g + h), IO<T>::ld(g + NH * H + h), IO<T>::ld(sc + h),
+    DynShared s = dyn_shared<IO<T>::kBf16>(IO<T>::ld(g + h), IO<T>::ld(g + NH * H + h), IO<T>::ld(sc + h),
                              IO<T>::ld(sc + H + h), IO<T>::ld(sc + 2 * H + h),
                              IO<T>::ld(sc + 3 * H + h), IO<T>::ld(sc + 4 * H + h),
                              log_dt_scale[h], freq, pos, c);
     for (int j = 0; j < NH; j++) {
         float a_re, a_im, vp;
-        dyn_pair(IO<T>::ld(g + j * H + h), IO<T>::ld(g + (NH + j) * H + h), freq, pos, s, a_re,
+        dyn_pair<IO<T>::kBf16>(IO<T>::ld(g + j * H + h), IO<T>::ld(g + (NH + j) * H + h), freq, pos, s, a_re,
                  a_im, vp);
         IO<T>::st(A_bar + idx * N + 2 * j, a_re);
         IO<T>::st(A_bar + idx * N + 2 * j + 1, a_im);
@@ -219,7 +219,7 @@ conv1d_silu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T
     for (int l = l0; l < lend; l++) {
         const float x3 = IO<T>::ld(x + base + (long long)l * Dm);
         const float yv = w0 * x0 + w1 * x1 + w2 * x2 + w3 * x3 + bv;
-        IO<T>::st(out + base + (long long)l * Dm, siluf_(yv));
+        IO<T>::st(out + base + (long long)l * Dm, siluf_<IO<T>::kBf16>(yv));
         x0 = x1;
         x1 = x2;
         x2 = x3;

@@ -134,12 +134,12 @@ __device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& 
             const T* gr = gate + bl * (long long)((a.N + 5) * H);
             const T* s5 = gr + a.N * H;
             const float pos = (float)(l + a.pos0);
-            DynShared ds = dyn_shared(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd),
+            DynShared ds = dyn_shared<IO<T>::kBf16>(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd),
                                       IO<T>::ld(s5 + hd), IO<T>::ld(s5 + H + hd),
                                       IO<T>::ld(s5 + 2 * H + hd), IO<T>::ld(s5 + 3 * H + hd),
                                       IO<T>::ld(s5 + 4 * H + hd), lds, freq, pos, a.dc);
             float vp;
-            dyn_pair(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds,
+            dyn_pair<IO<T>::kBf16>(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds,
                      ar, ai, vp);
             ar = IO<T>::rnd(ar);
             ai = IO<T>::rnd(ai);
@@ -435,12 +435,12 @@ decode_step_kernel(const DecodeArgs a) {
     const T* gr = static_cast<const T*>(a.gate_raw) + b * (long long)((a.N + 5) * H);
     const T* s5 = gr + a.N * H;
     const float freq = a.rope_freqs[hd], pos = (float)a.pos;
-    DynShared ds = dyn_shared(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd), IO<T>::ld(s5 + hd),
+    DynShared ds = dyn_shared<IO<T>::kBf16>(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd), IO<T>::ld(s5 + hd),
                               IO<T>::ld(s5 + H + hd), IO<T>::ld(s5 + 2 * H + hd),
                               IO<T>::ld(s5 + 3 * H + hd), IO<T>::ld(s5 + 4 * H + hd),
                               a.log_dt_scale[hd], freq, pos, a.dc);
     float a_re, a_im, vp;
-    dyn_pair(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds, a_re, a_im, vp);
+    dyn_pair<IO<T>::kBf16>(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds, a_re, a_im, vp);
     a_re = IO<T>::rnd(a_re);
     a_im = IO<T>::rnd(a_im);
     vp = IO<T>::rnd(vp);
@@ -513,13 +513,29 @@ static int launch_decode(const DecodeArgs& a, cudaStream_t st) {
 
 using namespace cdssm;
 
+namespace cdssm {   // scan_tc.cu
+bool scan_tc_supported(int D, int N, int C, int dtype);
+int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_raw, const float* log_dt_scale,
+                  const float* rope_freqs, const float* h0, void* y, float* final_state, int* status,
+                  const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, cudaStream_t st);
+}
+
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 extern "C" size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C) {
     if (B <= 0 || L <= 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1) || C <= 0) return 0;
     const size_t NC = ((size_t)L + C - 1) / C;
     const size_t units = (size_t)B * NC * H * (N / 2);
-    return align256(units * 2 * sizeof(float)) + align256(units * 2 * D * sizeof(float)) + 256;
+    return 256 + align256(units * 2 * sizeof(float)) + align256(units * 2 * D * sizeof(float));
+}
+
+extern "C" int cdssm_b200_scan_fused_status(const void* workspace, int* status_host, void* stream) {
+    if (!workspace || !status_host) return CDSSM_ERR_BAD_ARG;
+    if (int rc = check_cuda(cudaMemcpyAsync(status_host, workspace, sizeof(int), cudaMemcpyDeviceToHost,
+                                            (cudaStream_t)stream)))
+        return rc;
+    if (int rc = check_cuda(cudaStreamSynchronize((cudaStream_t)stream))) return rc;
+    return *status_host == 0 ? CDSSM_OK : CDSSM_ERR_TIMEOUT;
 }
 
 extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void* v,
@@ -531,7 +547,6 @@ extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const voi
                                          float adt_eps, float shortcut_scale, int B, int L, int H,
                                          int D, int N, int C, int pos0, int dtype, int flags,
                                          void* stream) {
-    (void)flags;
     if (!q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y) return CDSSM_ERR_BAD_ARG;
     if (B < 0 || L < 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1) || C <= 0) return CDSSM_ERR_BAD_ARG;
     if (dtype != CDSSM_BF16 && dtype != CDSSM_F32) return CDSSM_ERR_BAD_ARG;
@@ -540,6 +555,14 @@ extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const voi
     if (B == 0 || L == 0) return CDSSM_OK;
     const size_t need = cdssm_b200_scan_fused_workspace_bytes(B, L, H, D, N, C);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return CDSSM_ERR_WORKSPACE;
+    // first 256 bytes of the workspace: status word of the tensor-core kernel's bounded waits
+    int* status = static_cast<int*>(workspace);
+    if (!(flags & CDSSM_SCAN_FORCE_SIMT) && tail_state == nullptr && scan_tc_supported(D, N, C, dtype))
+        return scan_fused_tc(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state, status,
+                             DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps},
+                             shortcut_scale, B, L, H, pos0, (cudaStream_t)stream);
+    if (int rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(int), (cudaStream_t)stream))) return rc;
+    workspace = static_cast<char*>(workspace) + 256;
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.h0 = h0;

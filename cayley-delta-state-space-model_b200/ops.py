@@ -21,7 +21,7 @@ from ._lib import CdssmError, check
 
 __all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
            "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
-           "scan_fused_workspace_bytes", "CdssmError"]
+           "scan_fused_workspace_bytes", "scan_fused_status", "CdssmError"]
 
 _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
 
@@ -296,3 +296,22 @@ def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor
             adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, int(pos), _dtype_code(q),
             _stream()), "decode_step")
     return y
+
+
+def scan_fused_status(device=None) -> int:
+    """Status word of the last scan_fused call on this device and stream (synchronises the stream).
+    0 means every bounded device-side wait of the tensor-core kernel completed; anything else is
+    the code of the wait that ran out, and that call's outputs are undefined."""
+    import ctypes
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None:
+        return 0
+    out = ctypes.c_int(0)
+    ptr = buf.data_ptr() + ((-buf.data_ptr()) % 256)
+    with torch.cuda.device(device):
+        rc = _lib.lib().cdssm_b200_scan_fused_status(ptr, ctypes.addressof(out), key[1])
+    if rc not in (0, -5):
+        check(rc, "scan_fused_status")
+    return out.value

@@ -101,6 +101,8 @@ CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int 
  * dynamics -> L2-normalised q/k -> vp-scaled v -> chunked delta-rule scan in the reference's
  * chunk semantics (local scan from zero per chunk of C tokens, decay-only carry between chunks,
  * correction taken before each step) -> shortcut -> read-out with q -> sel_C gate.
+ * bf16, N = 2, D = C = 128 without tail_state runs the single-pass tcgen05/TMA kernel; every other
+ * supported size (even N <= 32, D <= 128, C <= 256, bf16 or fp32) the CUDA-core kernels.
  *   q,k (B,L,H,D) un-normalised; v (B,L,H,N) before the vp scale; gate_raw (B,L,(N+5)*H);
  *   h0 (B,H,N,D) float32 or NULL: carry into the first chunk;
  *   y (B,L,H,N); final_state (B,H,N,D) float32 or NULL: carry after the last chunk;
@@ -118,6 +120,13 @@ CDSSM_API int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void
                               float adt_delta, float adt_smoothness, float adt_eps,
                               float shortcut_scale, int B, int L, int H, int D, int N, int C,
                               int pos0, int dtype, int flags, void* stream);
+
+/* Reads back the status word a cdssm_b200_scan_fused_fwd call left at the start of its workspace
+ * (synchronises `stream`).  *status_host = 0 and CDSSM_OK if every bounded device-side wait of the
+ * tensor-core kernel completed; otherwise the code of the wait that ran out and
+ * CDSSM_ERR_TIMEOUT (the outputs of that call are then undefined; the context stays usable).
+ * No reference counterpart: the reference has no device-side waits. */
+CDSSM_API int cdssm_b200_scan_fused_status(const void* workspace, int* status_host, void* stream);
 
 /* One-token recurrent decode step for a batch of sequences: dynamics for position `pos`,
  * normalise q/k, state <- a (*) (state - beta (state k) k^T) + beta v k^T, y = sel_C * (state q

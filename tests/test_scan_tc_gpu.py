@@ -1,0 +1,64 @@
+"""The tcgen05/TMA single-pass scan kernel (bf16, N = 2, D = C = 128) against the CPU oracle and
+against the CUDA-core kernels, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from test_scan_gpu import oracle_scan, run_fused, unnormalise
+from util import BF16_TOL, rel_err, to_np
+
+pytestmark = pytest.mark.gpu
+N, C, D = 2, 128, 128
+
+
+def _inputs(orc, B, H, L, seed, scale=True):
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=seed, bf16=True, context_length=max(L, 2))
+    if scale:
+        inp = unnormalise(inp, np.random.default_rng(seed))
+        inp["q"], inp["k"] = orc.bf16_round(inp["q"]), orc.bf16_round(inp["k"])
+    return inp
+
+
+@pytest.mark.parametrize("B,H,L", [(1, 1, 128), (1, 2, 256), (2, 3, 300), (1, 2, 1), (1, 1, 129), (2, 5, 1024),
+                                   (3, 32, 512)])
+def test_tc_matches_oracle_and_simt(ops, orc, B, H, L):
+    inp = _inputs(orc, B, H, L, seed=L + H)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C)
+    assert ops.scan_fused_status() == 0
+    ys, fs = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.FORCE_SIMT)
+    wy, _ = oracle_scan(orc, inp, N, C, orc.ROUND_REFERENCE)
+    wy13, wf13 = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE)
+    assert rel_err(to_np(y), wy) <= BF16_TOL
+    assert rel_err(to_np(y), wy13) <= BF16_TOL / 2
+    assert rel_err(to_np(y), to_np(ys)) <= BF16_TOL / 2
+    scale = max(np.abs(wf13).max(), 1e-3)
+    assert np.abs(to_np(fin) - wf13).max() <= 2e-2 * scale
+    assert np.abs(to_np(fin) - to_np(fs)).max() <= 2e-2 * scale
+
+
+def test_tc_h0_shortcut_composition(ops, orc):
+    B, H, L = 2, 3, 512
+    inp = _inputs(orc, B, H, L, seed=77, scale=False)
+    h0 = np.random.default_rng(1).standard_normal((B, H, N, D)).astype(np.float32)
+    wy, wfin = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE, h0=h0, shortcut_scale=0.6)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6)
+    assert ops.scan_fused_status() == 0
+    assert rel_err(to_np(y), wy) <= BF16_TOL / 2
+    assert rel_err(to_np(fin), wfin) <= 2e-2
+    cut = lambda s: {k: (v[:, s] if getattr(v, "ndim", 0) >= 3 else v) for k, v in inp.items()}
+    y1, f1 = run_fused(ops, cut(slice(0, 256)), torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6)
+    y2, f2 = run_fused(ops, cut(slice(256, None)), torch.bfloat16, N, C, h0=to_np(f1), shortcut_scale=0.6, pos0=256)
+    assert torch.equal(torch.cat([y1, y2], 1), y) and torch.equal(f2, fin)
+
+
+def test_tc_deterministic_and_in_bounds(ops, orc):
+    B, H, L = 1, 4, 384
+    inp = _inputs(orc, B, H, L, seed=5)
+    n = B * L * H * N
+    big = torch.full((n + 512,), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = big[256:256 + n].view(B, L, H, N)
+    y1, f1 = run_fused(ops, inp, torch.bfloat16, N, C, out=out)
+    y1 = y1.clone()
+    y2, f2 = run_fused(ops, inp, torch.bfloat16, N, C)
+    assert torch.equal(y1, y2) and torch.equal(f1, f2)
+    assert bool((big[:256] == 7).all()) and bool((big[256 + n:] == 7).all())
