@@ -53,6 +53,10 @@ template <int kCols> struct RowSlice<__nv_bfloat16, kCols> {
             }
         }
     }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < kCols / 8; i++) v[i] = make_uint4(0, 0, 0, 0);
+    }
     __device__ __forceinline__ void get(float* f) const {
 #pragma unroll
         for (int i = 0; i < kCols / 8; i++) unpack8(v[i], f + 8 * i);
@@ -73,6 +77,10 @@ template <int kCols> struct RowSlice<float, kCols> {
                 s[i] = d < D ? __ldg(row + d) : 0.f;
             }
         }
+    }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < kCols / 4; i++) v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __device__ __forceinline__ void get(float* f) const {
         const float* s = reinterpret_cast<const float*>(v);
@@ -200,13 +208,20 @@ scan_walk_kernel(const ScanArgs a) {
     kraw.load(kbase, g, D, vec);
     if (kOutput) qraw.load(qbase, g, D, vec);
     const int so = ul * C;
-    for (int t = 0; t < Lc; t++) {
+    // The four units of a warp may sit in different chunks (a full one and the ragged last one):
+    // every lane walks the warp's longest chunk so that the shuffles stay warp-wide; beyond its
+    // own Lc a unit sees the zero padding of the reference (a = k = v = beta = 0, ssd.py:60-67).
+    const int Lw = __reduce_max_sync(0xffffffffu, Lc);
+    for (int t = 0; t < Lw; t++) {
         float kk[kCols], qq[kCols];
         kraw.get(kk);
         if (kOutput) qraw.get(qq);
         if (t + 1 < Lc) {
             kraw.load(kbase + (long long)(t + 1) * rstride, g, D, vec);
             if (kOutput) qraw.load(qbase + (long long)(t + 1) * rstride, g, D, vec);
+        } else {
+            kraw.zero();
+            if (kOutput) qraw.zero();
         }
         normalise<T, kCols>(kk);
         const float a_re = sm.a_re[so + t], a_im = sm.a_im[so + t], be = sm.beta[so + t];

@@ -46,8 +46,8 @@ struct __align__(1024) TcSmem {
     uint8_t s_tile[4096];         // UMMA B operand: rows 0,1 = bf16(s_re), bf16(s_im) over d
     uint8_t o_tile[4096];         // UMMA B operand: rows 0..3 = omega re/im hi, re/im lo over tokens
     float4 wx[kTcC];              // per token: V_t n_t w_t (xy) and V_t n_t x_t (zw)
-    float2 a[kTcC];               // per token decay a_t
-    float2 bp[4];                 // product of a over each 32-token block
+    float2 a[2][kTcC];            // per token decay a_t (double buffered by chunk parity)
+    float2 bp[2][4];              // product of a over each 32-token block
     uint64_t full_k[2], full_q, mma_gp0, mma_kr, mma_gp1, mma_ell;
     uint64_t gp0_free, gp1_free, s_ready, omega_ready, blk_done[3], bp_ready, drain;
     uint32_t tmem_base;
@@ -108,50 +108,80 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
     load_q(0);
     if (a.NC > 1) load_k(1);
 
-    for (int c = 0; c < a.NC; c++) {
-        const int st = c & 1;
-        const uint32_t ph = c & 1;
-        if (!mbar_wait(&sm.full_k[st], (c >> 1) & 1, ab)) { code = 1; break; }
-        pend_k[st] = false;
-        if (!mbar_wait(&sm.full_q, ph, ab)) { code = 2; break; }
-        pend_q = false;
-        if (c > 0 && !mbar_wait(&sm.gp1_free, (c - 1) & 1, ab)) { code = 3; break; }
-        tc_fence_after();
-        // pass 0: G[:, 0:64] = K K[0:64]^T ; P[:, 0:64] = Q K[0:64]^T
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColG, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
-        umma_commit(&sm.mma_gp0);
-        // kappa = K s^T, rho = Q s^T
-        if (!mbar_wait(&sm.s_ready, ph, ab)) { code = 4; break; }
-        tc_fence_after();
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColKappa, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColRho, kmaj(qaddr, kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
-        umma_commit(&sm.mma_kr);
-        // pass 1: columns 64..127 (rows 64..127 of the K tile as the B operand)
-        if (!mbar_wait(&sm.gp0_free, ph, ab)) { code = 5; break; }
-        tc_fence_after();
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColG, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
-        umma_commit(&sm.mma_gp1);
-        // the Q tile is free once pass 1 and rho have read it
-        if (!mbar_wait(&sm.mma_gp1, ph, ab)) { code = 6; break; }
-        if (c + 1 < a.NC) load_q(c + 1);
+    // Event loop: every task of every chunk is issued as soon as what it depends on has happened,
+    // so the Gram UMMAs of chunk c+1 and the TMA refills run under chunk c's CUDA-core work.
+    // A task's barrier is only polled before the event that could complete its NEXT phase has been
+    // triggered (each such event depends on the task itself), so parity tests cannot alias.
+    const int NC = a.NC;
+    int i_gp0 = 0, i_kr = 0, i_gp1 = 0, i_lq = 1, i_ell = 0, i_lk = 2;
+    bool k_ok = false, q_ok = false;              // tiles of chunk i_gp0 have landed
+    const uint64_t t0 = global_ns();
+    uint64_t last = t0;
+    auto par = [](int c) { return (uint32_t)(c & 1); };
+    while (i_ell < NC) {
+        bool progress = false;
+        if (i_gp0 < NC) {   // pass 0: G[:, 0:64] = K K[0:64]^T ; P[:, 0:64] = Q K[0:64]^T
+            const int c = i_gp0, st = c & 1;
+            if (!k_ok && mbar_test(&sm.full_k[st], (c >> 1) & 1)) { k_ok = true; pend_k[st] = false; }
+            if (!q_ok && mbar_test(&sm.full_q, par(c))) { q_ok = true; pend_q = false; }
+            if (k_ok && q_ok && (c == 0 || mbar_test(&sm.gp1_free, par(c - 1)))) {
+                tc_fence_after();
+                for (int j = 0; j < 8; j++)
+                    umma_bf16(tm + kColG, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
+                for (int j = 0; j < 8; j++)
+                    umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
+                umma_commit(&sm.mma_gp0);
+                i_gp0++; k_ok = q_ok = false; progress = true;
+            }
+        }
+        if (i_kr < i_gp0 && mbar_test(&sm.s_ready, par(i_kr))) {   // kappa = K s^T, rho = Q s^T
+            const int st = i_kr & 1;
+            tc_fence_after();
+            for (int j = 0; j < 8; j++)
+                umma_bf16(tm + kColKappa, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
+            for (int j = 0; j < 8; j++)
+                umma_bf16(tm + kColRho, kmaj(qaddr, kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
+            umma_commit(&sm.mma_kr);
+            i_kr++; progress = true;
+        }
+        if (i_gp1 < i_kr && mbar_test(&sm.gp0_free, par(i_gp1))) {   // pass 1: columns 64..127
+            const int st = i_gp1 & 1;
+            tc_fence_after();
+            for (int j = 0; j < 8; j++)
+                umma_bf16(tm + kColG, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
+            for (int j = 0; j < 8; j++)
+                umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
+            umma_commit(&sm.mma_gp1);
+            i_gp1++; progress = true;
+        }
+        // the Q tile is free once pass 1 (and, issued before it, rho) of its chunk have completed
+        if (i_lq <= i_gp1 && i_lq <= NC && mbar_test(&sm.mma_gp1, par(i_lq - 1))) {
+            if (i_lq < NC) load_q(i_lq);
+            i_lq++; progress = true;
+        }
         // l = K^T omega : A = K tile read MN-major (M = d: two 64-wide groups 16 KB apart; K = tokens,
         // 16 per step = 2 KB), B = omega tile (16 rows x 128 tokens, K-major)
-        if (!mbar_wait(&sm.omega_ready, ph, ab)) { code = 7; break; }
-        tc_fence_after();
-        for (int j = 0; j < 8; j++)
-            umma_bf16(tm + kColEll, umma_desc_sw128(kaddr[st] + (uint32_t)j * 2048, kSlabBytes, 1024),
-                      kmaj(oaddr, 2048, j, 0), idesc_el, j > 0);
-        umma_commit(&sm.mma_ell);
-        if (!mbar_wait(&sm.mma_ell, ph, ab)) { code = 8; break; }
-        if (c + 2 < a.NC) load_k(c + 2);
+        if (i_ell < i_gp1 && mbar_test(&sm.omega_ready, par(i_ell))) {
+            const int st = i_ell & 1;
+            tc_fence_after();
+            for (int j = 0; j < 8; j++)
+                umma_bf16(tm + kColEll, umma_desc_sw128(kaddr[st] + (uint32_t)j * 2048, kSlabBytes, 1024),
+                          kmaj(oaddr, 2048, j, 0), idesc_el, j > 0);
+            umma_commit(&sm.mma_ell);
+            i_ell++; progress = true;
+        }
+        // the K stage of chunk c is free once l_c has completed
+        if (i_lk - 2 < i_ell && i_lk - 2 < NC && mbar_test(&sm.mma_ell, par(i_lk - 2))) {
+            if (i_lk < NC) load_k(i_lk);
+            i_lk++; progress = true;
+        }
+        if (progress) {
+            last = global_ns();
+        } else if (*ab || global_ns() - last > kWaitLimitNs) {
+            code = 1 + (i_gp0 > i_kr) + 2 * (i_kr > i_gp1) + 4 * (i_gp1 > i_ell);
+            *ab = 1;
+            break;
+        }
     }
     if (code) {
         atomicCAS(a.status, 0, 100 + code);
@@ -185,8 +215,94 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 // ------------------------------------------------------------------------------------------
 // Compute warps: thread t owns token t of the chunk (TMEM lane t) and column d = t of the carry.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, int hd) {
+struct TokenCtx {          // per-token quantities of one chunk, produced by tc_prologue
+    cplx at, vg, W, W0, V, gpre, gsuf, gall, bp1, bp2;
+    float be, sc, mt;
+    bool valid;
+};
+
+// Everything of chunk c that does not depend on the carry or on tensor memory: dynamics of token t
+// (dynamics_fused.cu:64-139; vp scale of block.py:194-195), the in-block prefix / suffix products
+// of a, the block products, and |q_t|^-1 from the Q tile row.
+__device__ __forceinline__ bool tc_prologue(TcSmem& sm, const TcArgs& a, int b, int hd, int c, float lds,
+                                            float freq, TokenCtx& x) {
     using T = __nv_bfloat16;
+    volatile int* ab = &sm.abort_flag;
+    const int t = threadIdx.x, J = t >> 5, tl = t & 31, H = a.H, L = a.L;
+    const int l = c * kTcC + t;
+    x.valid = l < L;
+    x.at = {0.f, 0.f};
+    x.vg = {0.f, 0.f};
+    x.be = 0.f;
+    x.sc = 0.f;
+    if (x.valid) {
+        const size_t bl = (size_t)b * L + l;
+        const T* gr = a.gate_raw + bl * (size_t)(7 * H);
+        const float pos = (float)(l + a.pos0);
+        DynShared ds = dyn_shared<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), IO<T>::ld(gr + 2 * H + hd),
+                                        IO<T>::ld(gr + 3 * H + hd), IO<T>::ld(gr + 4 * H + hd),
+                                        IO<T>::ld(gr + 5 * H + hd), IO<T>::ld(gr + 6 * H + hd), lds, freq, pos, a.dc);
+        float vp;
+        dyn_pair<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), freq, pos, ds, x.at.r, x.at.i, vp);
+        x.at.r = bfr(x.at.r);
+        x.at.i = bfr(x.at.i);
+        vp = bfr(vp);
+        x.be = bfr(ds.beta);
+        x.sc = bfr(ds.sel_c);
+        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v + (bl * H + hd) * 2);
+        x.vg.r = bfr(__low2float(v2) * vp);
+        x.vg.i = bfr(__high2float(v2) * vp);
+    }
+    const int pb = c & 1;                                  // a / bp are double buffered by chunk parity
+    sm.a[pb][t] = make_float2(x.at.r, x.at.i);
+    cplx W = x.at, S = x.at;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
+        cplx dn = {__shfl_down_sync(0xffffffffu, S.r, o), __shfl_down_sync(0xffffffffu, S.i, o)};
+        if (tl >= o) W = cmul(W, up);
+        if (tl + o < 32) S = cmul(S, dn);
+    }
+    x.W = W;
+    x.W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
+    x.V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
+    if (tl == 0) x.W0 = {1.f, 0.f};
+    if (tl == 31) { x.V = {1.f, 0.f}; sm.bp[pb][J] = make_float2(W.r, W.i); }
+    __syncwarp();
+    if (tl == 0) mbar_arrive(&sm.bp_ready);
+    // |q_t|^-1 from the Q tile row (swizzled 16-byte chunks) while the other warps catch up
+    if (!warp_wait(&sm.full_q, c & 1, ab)) return false;
+    float qq = 0.f;
+#pragma unroll
+    for (int sl = 0; sl < 2; sl++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint4 r = *reinterpret_cast<const uint4*>(sm.q + sl * kSlabBytes + t * 128 + ((j ^ (t & 7)) << 4));
+            float f[8];
+            unpack8(r, f);
+#pragma unroll
+            for (int e = 0; e < 8; e++) qq += f[e] * f[e];
+        }
+    x.mt = rsqrtf(qq + kEps);
+    if (!warp_wait(&sm.bp_ready, c & 1, ab)) return false;
+    cplx bpv[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) bpv[i] = {sm.bp[pb][i].x, sm.bp[pb][i].y};
+    x.gpre = {1.f, 0.f};
+    x.gsuf = {1.f, 0.f};
+    x.gall = {1.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (i < J) x.gpre = cmul(x.gpre, bpv[i]);
+        if (i > J) x.gsuf = cmul(x.gsuf, bpv[i]);
+        x.gall = cmul(x.gall, bpv[i]);
+    }
+    x.bp1 = bpv[1];
+    x.bp2 = bpv[2];
+    return true;
+}
+
+__device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, int hd) {
     volatile int* ab = &sm.abort_flag;
     const int t = threadIdx.x, J = t >> 5, tl = t & 31;
     const int H = a.H, L = a.L;
@@ -208,73 +324,14 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
     __syncwarp();
     if (tl == 0) mbar_arrive(&sm.s_ready);
 
-    for (int c = 0; c < a.NC; c++) {
+    TokenCtx x;
+    if (!tc_prologue(sm, a, b, hd, 0, lds, freq, x)) code = 10;
+
+    for (int c = 0; c < a.NC && !code; c++) {
         const uint32_t ph = c & 1;
         const int l = c * kTcC + t;
-        const bool valid = l < L;
-        // ---- dynamics of token t (dynamics_fused.cu:64-139; vp scale of block.py:194-195)
-        cplx at = {0.f, 0.f};
-        float be = 0.f, sc = 0.f;
-        cplx vg = {0.f, 0.f};
-        if (valid) {
-            const size_t bl = (size_t)b * L + l;
-            const T* gr = a.gate_raw + bl * (size_t)(7 * H);
-            const float pos = (float)(l + a.pos0);
-            DynShared ds = dyn_shared<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), IO<T>::ld(gr + 2 * H + hd),
-                                            IO<T>::ld(gr + 3 * H + hd), IO<T>::ld(gr + 4 * H + hd),
-                                            IO<T>::ld(gr + 5 * H + hd), IO<T>::ld(gr + 6 * H + hd), lds, freq, pos, a.dc);
-            float vp;
-            dyn_pair<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), freq, pos, ds, at.r, at.i, vp);
-            at.r = bfr(at.r);
-            at.i = bfr(at.i);
-            vp = bfr(vp);
-            be = bfr(ds.beta);
-            sc = bfr(ds.sel_c);
-            const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v + (bl * H + hd) * 2);
-            vg.r = bfr(__low2float(v2) * vp);
-            vg.i = bfr(__high2float(v2) * vp);
-        }
-        sm.a[t] = make_float2(at.r, at.i);
-        // ---- in-block prefix (inclusive W, exclusive W0) and exclusive suffix V of a
-        cplx W = at, S = at;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
-            cplx dn = {__shfl_down_sync(0xffffffffu, S.r, o), __shfl_down_sync(0xffffffffu, S.i, o)};
-            if (tl >= o) W = cmul(W, up);
-            if (tl + o < 32) S = cmul(S, dn);
-        }
-        cplx W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
-        cplx V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
-        if (tl == 0) W0 = {1.f, 0.f};
-        if (tl == 31) { V = {1.f, 0.f}; sm.bp[J] = make_float2(W.r, W.i); }
-        __syncwarp();
-        if (tl == 0) mbar_arrive(&sm.bp_ready);
-        if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 10; break; }
-        cplx bpv[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) bpv[i] = {sm.bp[i].x, sm.bp[i].y};
-        cplx gpre = {1.f, 0.f}, gsuf = {1.f, 0.f}, gall = {1.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (i < J) gpre = cmul(gpre, bpv[i]);
-            if (i > J) gsuf = cmul(gsuf, bpv[i]);
-            gall = cmul(gall, bpv[i]);
-        }
-        // ---- |q_t|^-1 from the Q tile row (swizzled 16-byte chunks)
-        if (!warp_wait(&sm.full_q, ph, ab)) { code = 11; break; }
-        float qq = 0.f;
-#pragma unroll
-        for (int sl = 0; sl < 2; sl++)
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const uint4 r = *reinterpret_cast<const uint4*>(sm.q + sl * kSlabBytes + t * 128 + ((j ^ (t & 7)) << 4));
-                float f[8];
-                unpack8(r, f);
-#pragma unroll
-                for (int e = 0; e < 8; e++) qq += f[e] * f[e];
-            }
-        const float mt = rsqrtf(qq + kEps);
+        const cplx at = x.at, vg = x.vg, W = x.W, W0 = x.W0, V = x.V;
+        const float be = x.be, mt = x.mt;
         // ---- kappa_t = k_t.s, rho_t = q_t.s (raw rows; scaled by the norms below)
         if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
         tc_fence_after();
@@ -290,18 +347,18 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
         for (int I = 0; I <= J; I++) {
             if (!warp_wait(I < 2 ? &sm.mma_gp0 : &sm.mma_gp1, ph, ab)) { code = 13; fail = true; break; }
             tc_fence_after();
-            if (I < J) {
-                if (!warp_wait(&sm.blk_done[I], ph, ab)) { code = 14; fail = true; break; }
-                if (I > 0) { agw = cmul(agw, bpv[I]); agx = cmul(agx, bpv[I]); apw = cmul(apw, bpv[I]); apx = cmul(apx, bpv[I]); }
-            }
-            tmem_ld32(tlane + kColG + (I & 1) * 32, g);
-            tmem_ld32(tlane + kColP + (I & 1) * 32, p);
+            tmem_ld32x2(tlane + kColG + (I & 1) * 32, g, tlane + kColP + (I & 1) * 32, p);
             if (I == (J < 1 ? J : 1)) {   // this warp's last read of the first column half
                 tc_fence_before();
                 __syncwarp();
                 if (tl == 0) mbar_arrive(&sm.gp0_free);
             }
             if (I < J) {
+                if (!warp_wait(&sm.blk_done[I], ph, ab)) { code = 14; fail = true; break; }
+                if (I > 0) {
+                    const cplx bpI = I == 1 ? x.bp1 : x.bp2;
+                    agw = cmul(agw, bpI); agx = cmul(agx, bpI); apw = cmul(apw, bpI); apx = cmul(apx, bpI);
+                }
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     const float4 wx = sm.wx[I * 32 + i];
@@ -329,7 +386,7 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             cplx cur = {1.f, 0.f};
 #pragma unroll
             for (int i = 31; i >= 0; i--) {
-                const float2 ai = sm.a[J * 32 + i];
+                const float2 ai = sm.a[ph][J * 32 + i];
                 if (i < tl) {
                     gam0[i] = cur;
                     cur = cmul(cur, cplx{ai.x, ai.y});
@@ -339,7 +396,7 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             }
         }
         // unknowns u = n w and x~ = n x:  u_t = n_t b_t - sum_i (beta_t n_t^2 a_t Gamma0 G_raw) u_i
-        const cplx gam = cmul(gpre, W), gam_prev = cmul(gpre, W0);
+        const cplx gam = cmul(x.gpre, W), gam_prev = cmul(x.gpre, W0);
         const cplx wagw = cmul(W, agw), wagx = cmul(W, agx);
         const cplx gk = cmul(gam, kap);
         cplx cw = {nt * be * (vg.r - nt * wagw.r), nt * be * (vg.i - nt * wagw.i)};
@@ -360,27 +417,10 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             yin.r += p[i] * e.r;
             yin.i += p[i] * e.i;
         }
-        // ---- read-out: local + correction taken before the step (exact_correction.cu:90-94)
-        {
-            const cplx apwa = cmul(at, apw);
-            const cplx off = cmul(W0, cplx{apwa.r - apx.r, apwa.i - apx.i});
-            const cplx car = cmul(gam_prev, rho);
-            float yr = mt * (pd * cw.r + yin.r + off.r + car.r);
-            float yi = mt * (pd * cw.i + yin.i + off.i + car.i);
-            if (a.shortcut_scale != 0.f) {   // block.py:202-208
-                const float qk = mt * nt * pd;
-                yr += a.shortcut_scale * qk * qk * vg.r;
-                yi += a.shortcut_scale * qk * qk * vg.i;
-            }
-            if (valid) {
-                __nv_bfloat162 o = __floats2bfloat162_rn(bfr(yr) * sc, bfr(yi) * sc);
-                *reinterpret_cast<__nv_bfloat162*>(a.y + (((size_t)b * L + l) * H + hd) * 2) = o;
-            }
-        }
         // ---- publish V n w, V n x for the later blocks; omega = Gamma[C-1,t] n_t w_t for l
         const cplx wh = cmul(V, cw), xh = cmul(V, cx);
         sm.wx[t] = make_float4(wh.r, wh.i, xh.r, xh.i);
-        const cplx om = cmul(gsuf, wh);
+        const cplx om = cmul(x.gsuf, wh);
         {
             const float hr = bfr(om.r), hi = bfr(om.i);
             st_bf16(sm.o_tile, small_tile_off(0, t), hr);
@@ -394,6 +434,26 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             if (J < 3) mbar_arrive(&sm.blk_done[J]);
             mbar_arrive(&sm.omega_ready);
         }
+        // ---- read-out: local + correction taken before the step (exact_correction.cu:90-94)
+        {
+            const cplx apwa = cmul(at, apw);
+            const cplx off = cmul(W0, cplx{apwa.r - apx.r, apwa.i - apx.i});
+            const cplx car = cmul(gam_prev, rho);
+            float yr = mt * (pd * cw.r + yin.r + off.r + car.r);
+            float yi = mt * (pd * cw.i + yin.i + off.i + car.i);
+            if (a.shortcut_scale != 0.f) {   // block.py:202-208
+                const float qk = mt * nt * pd;
+                yr += a.shortcut_scale * qk * qk * vg.r;
+                yi += a.shortcut_scale * qk * qk * vg.i;
+            }
+            if (x.valid) {
+                __nv_bfloat162 o = __floats2bfloat162_rn(bfr(yr) * x.sc, bfr(yi) * x.sc);
+                *reinterpret_cast<__nv_bfloat162*>(a.y + (((size_t)b * L + l) * H + hd) * 2) = o;
+            }
+        }
+        // ---- next chunk's carry-independent work runs under the l UMMA
+        const cplx gall = x.gall;
+        if (c + 1 < a.NC && !tc_prologue(sm, a, b, hd, c + 1, lds, freq, x)) { code = 10; break; }
         // ---- carry: s <- bf16(gamma_C) s + bf16(l)   (inter_chunk_scan.cu:73-83 on bf16 inputs)
         if (!warp_wait(&sm.mma_ell, ph, ab)) { code = 15; break; }
         tc_fence_after();
@@ -459,7 +519,10 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(sm.tmem_base, kTmemCols);
+    if (warp == 4) {
+        __syncwarp();
+        tmem_dealloc(sm.tmem_base, kTmemCols);
+    }
 }
 
 

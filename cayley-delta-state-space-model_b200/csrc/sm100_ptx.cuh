@@ -37,12 +37,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  `abort_flag` (shared memory) lets one role that gave up release all the others.
-constexpr uint32_t kWaitLimit = 1u << 21;   // x (up to ~1 us suspend) => seconds at most
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {   // non-blocking
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kWaitLimitNs of wall time (the global nanosecond timer), so a
+// protocol error costs a fraction of a second, never a hung GPU.  `abort_flag` (shared memory)
+// lets one role that gave up release all the others.
+constexpr uint64_t kWaitLimitNs = 400ull * 1000 * 1000;
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < kWaitLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t i = 0;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 63 && *abort_flag) return false;
+        if ((i & 15) == 15) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) break;
+        }
     }
     *abort_flag = 1;
     return false;
@@ -142,6 +165,31 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* r) {
           "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]),
           "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
         : "r"(taddr)
+        : "memory");
+}
+// Two 32-column loads in flight together, one wait.
+__device__ __forceinline__ void tmem_ld32x2(uint32_t ta, float* ra, uint32_t tb, float* rb) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(ra);
+    uint32_t* w = reinterpret_cast<uint32_t*>(rb);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]),
+          "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]),
+          "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]),
+          "=r"(u[29]), "=r"(u[30]), "=r"(u[31]),
+          "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]),
+          "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]),
+          "=r"(w[15]), "=r"(w[16]), "=r"(w[17]), "=r"(w[18]), "=r"(w[19]), "=r"(w[20]), "=r"(w[21]),
+          "=r"(w[22]), "=r"(w[23]), "=r"(w[24]), "=r"(w[25]), "=r"(w[26]), "=r"(w[27]), "=r"(w[28]),
+          "=r"(w[29]), "=r"(w[30]), "=r"(w[31])
+        : "r"(ta), "r"(tb)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float* r) {

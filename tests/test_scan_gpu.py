@@ -65,7 +65,7 @@ def test_fused_bf16_vs_reference_rounding(ops, orc, B, H, L, D, N, C):
     assert rel_err(to_np(y), wy) <= BF16_TOL
     wy13, wfin13 = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE)  # same rounding points as the kernel
     assert rel_err(to_np(y), wy13) <= BF16_TOL / 2
-    assert np.abs(to_np(fin) - wfin13).max() <= 1e-3 * max(np.abs(wfin13).max(), 1e-3)
+    assert np.abs(to_np(fin) - wfin13).max() <= 1e-2 * max(np.abs(wfin13).max(), 1e-3)
 
 
 @pytest.mark.parametrize("dtype,mask,tol", [(torch.float32, 0, FP32_TOL), (torch.bfloat16, 13, 2.0 ** -7)])
