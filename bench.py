@@ -198,7 +198,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (1 = force the CUDA-core kernels)")
+    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (2 = the single-pass tcgen05/TMA kernel)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -304,10 +304,11 @@ def main():
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic", "config": workload_config(args.workload, w),
                 "clocks": clocks.summary(t_begin, t_end), "e2e": e2e,
-                "gpu_launches": 3 * args.steps,
+                "gpu_launches": (1 if args.flags & 2 else 3) * args.steps,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                             "kernel": "the whole step (local pass + carry pass + output pass)",
+                             "kernel": ("scan_tc_kernel (single pass)" if args.flags & 2 else
+                                        "the whole step (scan_walk local pass + scan_carry + scan_walk output pass)"),
                              "algorithmic_bytes_per_launch": abytes}}
         if not args.no_cpu_baseline and world == 1:
             tps, dt_s, s, _ = run_cpu_oracle(w, 5, 1)

@@ -572,7 +572,12 @@ extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const voi
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return CDSSM_ERR_WORKSPACE;
     // first 256 bytes of the workspace: status word of the tensor-core kernel's bounded waits
     int* status = static_cast<int*>(workspace);
-    if (!(flags & CDSSM_SCAN_FORCE_SIMT) && tail_state == nullptr && scan_tc_supported(D, N, C, dtype))
+    // The tensor-core kernel is selected explicitly: as measured on B200 it is still slower than
+    // the CUDA-core kernels at the benchmark sizes (one sequential chain per CTA leaves the SM idle).
+    if ((flags & CDSSM_SCAN_TENSOR_CORE) && !(flags & CDSSM_SCAN_FORCE_SIMT)) {
+        if (tail_state != nullptr || !scan_tc_supported(D, N, C, dtype)) return CDSSM_ERR_UNSUPPORTED;
+    }
+    if ((flags & CDSSM_SCAN_TENSOR_CORE) && !(flags & CDSSM_SCAN_FORCE_SIMT))
         return scan_fused_tc(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state, status,
                              DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps},
                              shortcut_scale, B, L, H, pos0, (cudaStream_t)stream);

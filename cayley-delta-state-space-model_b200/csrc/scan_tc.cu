@@ -60,6 +60,7 @@ struct TcArgs {
     __nv_bfloat16* y;
     float* final_state;
     int* status;                  // device word: 0 ok, else the code of the wait that ran out
+    long long* trace;             // optional: per-phase clock64 stamps of CTA 0 (performance debugging)
     DynConsts dc;
     float shortcut_scale;
     int B, L, H, NC, pos0;
@@ -117,6 +118,7 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
     bool k_ok = false, q_ok = false;              // tiles of chunk i_gp0 have landed
     const uint64_t t0 = global_ns();
     uint64_t last = t0;
+    uint32_t idle = 0;
     auto par = [](int c) { return (uint32_t)(c & 1); };
     while (i_ell < NC) {
         bool progress = false;
@@ -131,6 +133,7 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
                 for (int j = 0; j < 8; j++)
                     umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
                 umma_commit(&sm.mma_gp0);
+                if (a.trace && blockIdx.x == 0 && c < 8) a.trace[(c * 5 + 4) * 16 + 0] = clock64();
                 i_gp0++; k_ok = q_ok = false; progress = true;
             }
         }
@@ -142,6 +145,7 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColRho, kmaj(qaddr, kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
             umma_commit(&sm.mma_kr);
+            if (a.trace && blockIdx.x == 0 && i_kr < 8) a.trace[(i_kr * 5 + 4) * 16 + 1] = clock64();
             i_kr++; progress = true;
         }
         if (i_gp1 < i_kr && mbar_test(&sm.gp0_free, par(i_gp1))) {   // pass 1: columns 64..127
@@ -152,6 +156,7 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
             umma_commit(&sm.mma_gp1);
+            if (a.trace && blockIdx.x == 0 && i_gp1 < 8) a.trace[(i_gp1 * 5 + 4) * 16 + 2] = clock64();
             i_gp1++; progress = true;
         }
         // the Q tile is free once pass 1 (and, issued before it, rho) of its chunk have completed
@@ -168,6 +173,7 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
                 umma_bf16(tm + kColEll, umma_desc_sw128(kaddr[st] + (uint32_t)j * 2048, kSlabBytes, 1024),
                           kmaj(oaddr, 2048, j, 0), idesc_el, j > 0);
             umma_commit(&sm.mma_ell);
+            if (a.trace && blockIdx.x == 0 && i_ell < 8) a.trace[(i_ell * 5 + 4) * 16 + 3] = clock64();
             i_ell++; progress = true;
         }
         // the K stage of chunk c is free once l_c has completed
@@ -177,6 +183,8 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
         }
         if (progress) {
             last = global_ns();
+        } else if ((++idle & 7) != 0) {
+            __nanosleep(32);          // do not steal issue slots from the compute warp on this scheduler
         } else if (*ab || global_ns() - last > kWaitLimitNs) {
             code = 1 + (i_gp0 > i_kr) + 2 * (i_kr > i_gp1) + 4 * (i_gp1 > i_ell);
             *ab = 1;
@@ -302,6 +310,7 @@ __device__ __forceinline__ bool tc_prologue(TcSmem& sm, const TcArgs& a, int b, 
     return true;
 }
 
+#define TC_STAMP(idx) do { if (a.trace && blockIdx.x == 0 && tl == 0 && c < 8) a.trace[(c * 5 + J) * 16 + (idx)] = clock64(); } while (0)
 __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, int hd) {
     volatile int* ab = &sm.abort_flag;
     const int t = threadIdx.x, J = t >> 5, tl = t & 31;
@@ -332,14 +341,7 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
         const int l = c * kTcC + t;
         const cplx at = x.at, vg = x.vg, W = x.W, W0 = x.W0, V = x.V;
         const float be = x.be, mt = x.mt;
-        // ---- kappa_t = k_t.s, rho_t = q_t.s (raw rows; scaled by the norms below)
-        if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
-        tc_fence_after();
-        float kr4[4], rr4[4];
-        tmem_ld4(tlane + kColKappa, kr4);
-        tmem_ld4(tlane + kColRho, rr4);
-        const cplx kap = {kr4[0], kr4[1]}, rho = {rr4[0], rr4[1]};
-
+        TC_STAMP(0);
         // ---- column blocks I = 0..J
         cplx agw = {0, 0}, agx = {0, 0}, apw = {0, 0}, apx = {0, 0};
         float g[32], p[32];
@@ -368,6 +370,7 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             }
         }
         if (fail) break;
+        TC_STAMP(2);
         // every TMEM read of this chunk's G/P is done
         tc_fence_before();
         __syncwarp();
@@ -380,43 +383,49 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             if (i == tl) { gd = g[i]; pd = p[i]; }
         }
         const float nt = rsqrtf(gd + kEps);                  // |k_t|^-1 from the Gram diagonal
-        // Gamma0[t,i] = prod a_r, i < r <= t-1, for the columns of this block (0 for i >= t)
-        cplx gam0[32];
+        // Phase A (no dependence on other lanes): coefficients of the unit-lower-triangular system
+        // for the unknowns u = n w and x~ = n x,
+        //   u_t = n_t b_t - sum_{i<t} cc[i] u_i,  cc[i] = beta_t n_t^2 a_t Gamma0[t,i] G_raw[t,i],
+        // Gamma0[t,i] = prod a_r, i < r <= t-1, built leftwards from the diagonal (0 for i >= t).
+        const float bnn = be * nt * nt;
+        const cplx f = {bnn * at.r, bnn * at.i};
+        cplx cc[32];
         {
             cplx cur = {1.f, 0.f};
 #pragma unroll
             for (int i = 31; i >= 0; i--) {
                 const float2 ai = sm.a[ph][J * 32 + i];
-                if (i < tl) {
-                    gam0[i] = cur;
-                    cur = cmul(cur, cplx{ai.x, ai.y});
-                } else {
-                    gam0[i] = {0.f, 0.f};
-                }
+                const bool on = i < tl;
+                const cplx fg = cmul(f, cur);
+                cc[i] = {on ? fg.r * g[i] : 0.f, on ? fg.i * g[i] : 0.f};
+                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
             }
         }
-        // unknowns u = n w and x~ = n x:  u_t = n_t b_t - sum_i (beta_t n_t^2 a_t Gamma0 G_raw) u_i
+        TC_STAMP(3);
+        // ---- kappa_t = k_t.s, rho_t = q_t.s (raw rows; scaled by the norms)
+        if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
+        tc_fence_after();
+        TC_STAMP(1);
+        float kr4[4], rr4[4];
+        tmem_ld4(tlane + kColKappa, kr4);
+        tmem_ld4(tlane + kColRho, rr4);
+        const cplx kap = {kr4[0], kr4[1]}, rho = {rr4[0], rr4[1]};
         const cplx gam = cmul(x.gpre, W), gam_prev = cmul(x.gpre, W0);
         const cplx wagw = cmul(W, agw), wagx = cmul(W, agx);
         const cplx gk = cmul(gam, kap);
         cplx cw = {nt * be * (vg.r - nt * wagw.r), nt * be * (vg.i - nt * wagw.i)};
         cplx cx = {nt * be * (nt * gk.r - nt * wagx.r), nt * be * (nt * gk.i - nt * wagx.i)};
-        const float bnn = be * nt * nt;
-        const cplx f = {bnn * at.r, bnn * at.i};
-        cplx yin = {0.f, 0.f};
+        // Phase B: the sequential substitution, nothing else in the loop
 #pragma unroll
         for (int i = 0; i < 32; i++) {
             const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
-            const cplx fg = cmul(f, gam0[i]);
-            const cplx cc = {fg.r * g[i], fg.i * g[i]};
-            const cplx d1 = cmul(cc, uw), d2 = cmul(cc, ux);
-            cw.r -= d1.r; cw.i -= d1.i;
-            cx.r -= d2.r; cx.i -= d2.i;
-            const cplx au = cmul(at, uw);
-            const cplx e = cmul(gam0[i], cplx{au.r - ux.r, au.i - ux.i});
-            yin.r += p[i] * e.r;
-            yin.i += p[i] * e.i;
+            cw.r -= cc[i].r * uw.r - cc[i].i * uw.i;
+            cw.i -= cc[i].r * uw.i + cc[i].i * uw.r;
+            cx.r -= cc[i].r * ux.r - cc[i].i * ux.i;
+            cx.i -= cc[i].r * ux.i + cc[i].i * ux.r;
         }
+        TC_STAMP(4);
         // ---- publish V n w, V n x for the later blocks; omega = Gamma[C-1,t] n_t w_t for l
         const cplx wh = cmul(V, cw), xh = cmul(V, cx);
         sm.wx[t] = make_float4(wh.r, wh.i, xh.r, xh.i);
@@ -433,6 +442,25 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
         if (tl == 0) {
             if (J < 3) mbar_arrive(&sm.blk_done[J]);
             mbar_arrive(&sm.omega_ready);
+        }
+        // Phase C (off the other warps' critical path): in-block part of the read-out,
+        // sum_{i<t} P_raw[t,i] Gamma0[t,i] (a_t u_i - x~_i)
+        cplx yin = {0.f, 0.f};
+        {
+            cplx cur = {1.f, 0.f};
+#pragma unroll
+            for (int i = 31; i >= 0; i--) {
+                const float2 ai = sm.a[ph][J * 32 + i];
+                const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+                const bool on = i < tl;
+                const cplx au = cmul(at, uw);
+                const cplx e = cmul(cur, cplx{au.r - ux.r, au.i - ux.i});
+                const float pi = on ? p[i] : 0.f;
+                yin.r += pi * e.r;
+                yin.i += pi * e.i;
+                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+            }
         }
         // ---- read-out: local + correction taken before the step (exact_correction.cu:90-94)
         {
@@ -451,12 +479,15 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
                 *reinterpret_cast<__nv_bfloat162*>(a.y + (((size_t)b * L + l) * H + hd) * 2) = o;
             }
         }
+        TC_STAMP(5);
         // ---- next chunk's carry-independent work runs under the l UMMA
         const cplx gall = x.gall;
         if (c + 1 < a.NC && !tc_prologue(sm, a, b, hd, c + 1, lds, freq, x)) { code = 10; break; }
         // ---- carry: s <- bf16(gamma_C) s + bf16(l)   (inter_chunk_scan.cu:73-83 on bf16 inputs)
+        TC_STAMP(6);
         if (!warp_wait(&sm.mma_ell, ph, ab)) { code = 15; break; }
         tc_fence_after();
+        TC_STAMP(7);
         float e4[4];
         tmem_ld4(tlane + kColEll, e4);
         {
@@ -473,6 +504,7 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
         tc_fence_before();
         __syncwarp();
         if (tl == 0) mbar_arrive(&sm.s_ready);
+        TC_STAMP(8);
     }
     if (code) {
         if (tl == 0) atomicCAS(a.status, 0, 200 + code);
@@ -558,6 +590,9 @@ static bool make_tile_map(CUtensorMap* m, const void* base, int B, int L, int H)
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static long long* g_trace = nullptr;
+void scan_tc_set_trace(long long* p) { g_trace = p; }
+
 bool scan_tc_supported(int D, int N, int C, int dtype) {
     return dtype == CDSSM_BF16 && N == 2 && D == kTcD && C == kTcC;
 }
@@ -581,7 +616,7 @@ int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_
     a.gate_raw = static_cast<const __nv_bfloat16*>(gate_raw);
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.h0 = h0;
     a.y = static_cast<__nv_bfloat16*>(y);
-    a.final_state = final_state; a.status = status;
+    a.final_state = final_state; a.status = status; a.trace = g_trace;
     a.dc = dc; a.shortcut_scale = shortcut_scale;
     a.B = B; a.L = L; a.H = H; a.NC = (L + kTcC - 1) / kTcC; a.pos0 = pos0;
     scan_tc_kernel<<<B * H, kTcThreads, smem, st>>>(tmK, tmQ, a);

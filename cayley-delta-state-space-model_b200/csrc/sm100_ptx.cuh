@@ -58,11 +58,17 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // Poll without a suspend hint: a hinted try_wait was measured to sleep for the whole hint
+    // (about a microsecond per hand-off), which dominated the chunk time.
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
+        if (mbar_test(bar, parity)) return true;
     const uint64_t t0 = global_ns();
+#pragma unroll 1
     for (uint32_t i = 0;; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 15) == 15) {
+        if (mbar_test(bar, parity)) return true;
+        __nanosleep(32);
+        if ((i & 31) == 31) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > kWaitLimitNs) break;
         }

@@ -195,6 +195,7 @@ class ExactCorrectionFn(Function):
 # Level 2: the fused path
 # ------------------------------------------------------------------------------------------
 FORCE_SIMT = 1
+TENSOR_CORE = 2
 
 _workspaces = {}
 

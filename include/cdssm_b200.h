@@ -92,7 +92,9 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
 
 /* Flags of cdssm_b200_scan_fused_fwd. */
 #define CDSSM_SCAN_DEFAULT 0
-#define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels even where the tensor-core one applies */
+#define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels (the default) */
+#define CDSSM_SCAN_TENSOR_CORE 2   /* use the single-pass tcgen05/TMA kernel: bf16, N = 2, D = C = 128,
+                                      no tail_state; CDSSM_ERR_UNSUPPORTED for other sizes */
 
 /* Bytes of workspace cdssm_b200_scan_fused_fwd needs for these sizes (0 on bad sizes). */
 CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C);
@@ -101,8 +103,8 @@ CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int 
  * dynamics -> L2-normalised q/k -> vp-scaled v -> chunked delta-rule scan in the reference's
  * chunk semantics (local scan from zero per chunk of C tokens, decay-only carry between chunks,
  * correction taken before each step) -> shortcut -> read-out with q -> sel_C gate.
- * bf16, N = 2, D = C = 128 without tail_state runs the single-pass tcgen05/TMA kernel; every other
- * supported size (even N <= 32, D <= 128, C <= 256, bf16 or fp32) the CUDA-core kernels.
+ * Supported: even N <= 32, D <= 128, C <= 256, bf16 or fp32 (CUDA-core kernels, three launches);
+ * with CDSSM_SCAN_TENSOR_CORE: bf16, N = 2, D = C = 128 in one single-pass tcgen05/TMA kernel.
  *   q,k (B,L,H,D) un-normalised; v (B,L,H,N) before the vp scale; gate_raw (B,L,(N+5)*H);
  *   h0 (B,H,N,D) float32 or NULL: carry into the first chunk;
  *   y (B,L,H,N); final_state (B,H,N,D) float32 or NULL: carry after the last chunk;

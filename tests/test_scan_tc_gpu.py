@@ -23,7 +23,7 @@ def _inputs(orc, B, H, L, seed, scale=True):
                                    (3, 32, 512)])
 def test_tc_matches_oracle_and_simt(ops, orc, B, H, L):
     inp = _inputs(orc, B, H, L, seed=L + H)
-    y, fin = run_fused(ops, inp, torch.bfloat16, N, C)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.TENSOR_CORE)
     assert ops.scan_fused_status() == 0
     ys, fs = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.FORCE_SIMT)
     wy, _ = oracle_scan(orc, inp, N, C, orc.ROUND_REFERENCE)
@@ -41,13 +41,13 @@ def test_tc_h0_shortcut_composition(ops, orc):
     inp = _inputs(orc, B, H, L, seed=77, scale=False)
     h0 = np.random.default_rng(1).standard_normal((B, H, N, D)).astype(np.float32)
     wy, wfin = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE, h0=h0, shortcut_scale=0.6)
-    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6, flags=ops.TENSOR_CORE)
     assert ops.scan_fused_status() == 0
     assert rel_err(to_np(y), wy) <= BF16_TOL / 2
     assert rel_err(to_np(fin), wfin) <= 2e-2
     cut = lambda s: {k: (v[:, s] if getattr(v, "ndim", 0) >= 3 else v) for k, v in inp.items()}
-    y1, f1 = run_fused(ops, cut(slice(0, 256)), torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6)
-    y2, f2 = run_fused(ops, cut(slice(256, None)), torch.bfloat16, N, C, h0=to_np(f1), shortcut_scale=0.6, pos0=256)
+    y1, f1 = run_fused(ops, cut(slice(0, 256)), torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6, flags=ops.TENSOR_CORE)
+    y2, f2 = run_fused(ops, cut(slice(256, None)), torch.bfloat16, N, C, h0=to_np(f1), shortcut_scale=0.6, pos0=256, flags=ops.TENSOR_CORE)
     assert torch.equal(torch.cat([y1, y2], 1), y) and torch.equal(f2, fin)
 
 
@@ -57,8 +57,14 @@ def test_tc_deterministic_and_in_bounds(ops, orc):
     n = B * L * H * N
     big = torch.full((n + 512,), 7.0, device="cuda", dtype=torch.bfloat16)
     out = big[256:256 + n].view(B, L, H, N)
-    y1, f1 = run_fused(ops, inp, torch.bfloat16, N, C, out=out)
+    y1, f1 = run_fused(ops, inp, torch.bfloat16, N, C, out=out, flags=ops.TENSOR_CORE)
     y1 = y1.clone()
-    y2, f2 = run_fused(ops, inp, torch.bfloat16, N, C)
+    y2, f2 = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.TENSOR_CORE)
     assert torch.equal(y1, y2) and torch.equal(f1, f2)
     assert bool((big[:256] == 7).all()) and bool((big[256 + n:] == 7).all())
+
+
+def test_tc_flag_rejects_unsupported_sizes(ops, orc):
+    inp = orc.make_inputs(1, 2, 64, 64, N=2, seed=1, bf16=True)
+    with pytest.raises(RuntimeError):
+        run_fused(ops, inp, torch.bfloat16, 2, 64, flags=ops.TENSOR_CORE)
