@@ -223,51 +223,70 @@ scan_walk_kernel(const ScanArgs a) {
             kraw.zero();
             if (kOutput) qraw.zero();
         }
-        normalise<T, kCols>(kk);
         const float a_re = sm.a_re[so + t], a_im = sm.a_im[so + t], be = sm.beta[so + t];
         const float vr = sm.v_re[so + t], vi = sm.v_im[so + t];
-        float yr = 0.f, yi = 0.f, qk = 0.f;
-        if (kOutput) {
-            normalise<T, kCols>(qq);
-            // correction is read BEFORE its step (exact_correction.cu:90-94)
-#pragma unroll
-            for (int i = 0; i < kCols; i++) { yr += rr[i] * qq[i]; yi += ri[i] * qq[i]; }
-            float wr = 0.f, wi = 0.f;
-#pragma unroll
-            for (int i = 0; i < kCols; i++) { wr += rr[i] * kk[i]; wi += ri[i] * kk[i]; }
-            wr = be * group_sum(wr);
-            wi = be * group_sum(wi);
-#pragma unroll
-            for (int i = 0; i < kCols; i++) {
-                const float er = rr[i] - wr * kk[i], ei = ri[i] - wi * kk[i];
-                rr[i] = a_re * er - a_im * ei;
-                ri[i] = a_re * ei + a_im * er;
-            }
-        }
-        float ur = 0.f, ui = 0.f;
-#pragma unroll
-        for (int i = 0; i < kCols; i++) { ur += zr[i] * kk[i]; ui += zi[i] * kk[i]; }
-        ur = be * group_sum(ur);
-        ui = be * group_sum(ui);
-        const float ivr = be * vr, ivi = be * vi;
+        // The rows stay raw; the normalisation (normalize_kq.cu:46-79) enters through the scalars
+        // ik = |k|^-1, iq = |q|^-1:  k^ = ik k, q^ = iq q.  Every dot product of the step is taken
+        // against the state BEFORE the update, so all reductions are issued together; the
+        // post-step read-out follows from  z' = a z + Kz k  =>  z'.q = a (z.q) + Kz (k.q).
+        // (The reference rounds k^ and q^ to bf16 before use; here they keep fp32 precision.)
+        float skk = 0.f, zkr = 0.f, zki = 0.f;
 #pragma unroll
         for (int i = 0; i < kCols; i++) {
-            const float er = zr[i] - ur * kk[i], ei = zi[i] - ui * kk[i];
-            zr[i] = a_re * er - a_im * ei + ivr * kk[i];
-            zi[i] = a_re * ei + a_im * er + ivi * kk[i];
+            skk += kk[i] * kk[i];
+            zkr += zr[i] * kk[i];
+            zki += zi[i] * kk[i];
+        }
+        float sqq = 0.f, kq = 0.f, zqr = 0.f, zqi = 0.f, rkr = 0.f, rki = 0.f, rqr = 0.f, rqi = 0.f;
+        if (kOutput) {
+#pragma unroll
+            for (int i = 0; i < kCols; i++) {
+                sqq += qq[i] * qq[i];
+                kq += kk[i] * qq[i];
+                zqr += zr[i] * qq[i];
+                zqi += zi[i] * qq[i];
+                rkr += rr[i] * kk[i];
+                rki += ri[i] * kk[i];
+                rqr += rr[i] * qq[i];
+                rqi += ri[i] * qq[i];
+            }
+        }
+        skk = group_sum(skk); zkr = group_sum(zkr); zki = group_sum(zki);
+        if (kOutput) {
+            sqq = group_sum(sqq); kq = group_sum(kq); zqr = group_sum(zqr); zqi = group_sum(zqi);
+            rkr = group_sum(rkr); rki = group_sum(rki); rqr = group_sum(rqr); rqi = group_sum(rqi);
+        }
+        const float ik = rsqrtf(skk + kEps);
+        const float bik = be * ik, bik2 = bik * ik;
+        // z' = a (z - beta (z.k^) k^) + beta v k^ = a z + Kz k
+        const float czr = bik2 * zkr, czi = bik2 * zki;
+        const float Kzr = bik * vr - (a_re * czr - a_im * czi);
+        const float Kzi = bik * vi - (a_re * czi + a_im * czr);
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const float x = zr[i], y = zi[i];
+            zr[i] = a_re * x - a_im * y + Kzr * kk[i];
+            zi[i] = a_re * y + a_im * x + Kzi * kk[i];
         }
         const float ncr = a_re * cr - a_im * ci, nci = a_re * ci + a_im * cr;
         cr = ncr;
         ci = nci;
         if (kOutput) {
+            const float iq = rsqrtf(sqq + kEps);
+            // correction is read BEFORE its step (exact_correction.cu:90-94), the local state after
+            float yr = iq * (rqr + a_re * zqr - a_im * zqi + Kzr * kq);
+            float yi = iq * (rqi + a_re * zqi + a_im * zqr + Kzi * kq);
+            // r' = a (r - beta (r.k^) k^) = a r + Kr k
+            const float crr = bik2 * rkr, cri = bik2 * rki;
+            const float Krr = -(a_re * crr - a_im * cri), Kri = -(a_re * cri + a_im * crr);
 #pragma unroll
-            for (int i = 0; i < kCols; i++) { yr += zr[i] * qq[i]; yi += zi[i] * qq[i]; }
-            yr = group_sum(yr);
-            yi = group_sum(yi);
-            if (a.shortcut_scale != 0.f) {   // block.py:202-208: sum_d shortcut[s,d] q[d] = (q.k)^2 v[s]
-#pragma unroll
-                for (int i = 0; i < kCols; i++) qk += qq[i] * kk[i];
-                qk = group_sum(qk);
+            for (int i = 0; i < kCols; i++) {
+                const float x = rr[i], y = ri[i];
+                rr[i] = a_re * x - a_im * y + Krr * kk[i];
+                ri[i] = a_re * y + a_im * x + Kri * kk[i];
+            }
+            if (a.shortcut_scale != 0.f) {   // block.py:202-208: sum_d shortcut[s,d] q[d] = (q^.k^)^2 v[s]
+                const float qk = iq * ik * kq;
                 const float f = a.shortcut_scale * qk * qk;
                 yr += f * vr;
                 yi += f * vi;
