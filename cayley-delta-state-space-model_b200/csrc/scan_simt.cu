@@ -166,7 +166,7 @@ __device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& 
 
 // kOutput = false: local pass (z only).  kOutput = true: output pass (z, r, read-out).
 template <typename T, int kCols, bool kOutput>
-__global__ void __launch_bounds__(kSimtThreads)
+__global__ void __launch_bounds__(kSimtThreads, (kOutput && kCols == 16) ? 4 : 1)
 scan_walk_kernel(const ScanArgs a) {
     extern __shared__ float smem[];
     ChunkScalars sm(smem, a.C);
