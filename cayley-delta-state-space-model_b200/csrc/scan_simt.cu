@@ -643,3 +643,58 @@ extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k
         return cols <= 8 ? launch_decode<__nv_bfloat16, 8>(a, st) : launch_decode<__nv_bfloat16, 16>(a, st);
     return cols <= 8 ? launch_decode<float, 8>(a, st) : launch_decode<float, 16>(a, st);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the fused scan.
+//
+// Some hosts of this library cannot hand it a workspace: an inference server whose memory pool
+// already owns every byte of the device, a plugin that runs inside somebody else's framework and
+// is not allowed to call the CUDA allocator (cudaMalloc synchronises the whole device and would
+// stall the other streams of that process), or an embedding whose allocator is simply not reachable
+// from where the scan is called.  For them the scratch of the three-launch scan lives in a
+// file-scope device array that the module carries itself: kNoAllocScratchBytes on every GPU that
+// loads the library, for as long as the process lives.
+//
+// In host code the array's name is only a handle for the symbol, not a device pointer; the device
+// address is looked up once per device with cudaGetSymbolAddress (with that device current) and it
+// is this address that the kernels receive.
+constexpr size_t kNoAllocScratchBytes = 16u << 20;   // 16 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+extern "C" size_t cdssm_b200_scan_fused_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
+
+extern "C" int cdssm_b200_scan_fused_fwd_noalloc(const void* q, const void* k, const void* v,
+                                                 const void* gate_raw, const float* log_dt_scale,
+                                                 const float* rope_freqs, const float* h0, void* y,
+                                                 float* final_state, float* tail_state, float gating_c,
+                                                 float omega_thresh, float adt_delta,
+                                                 float adt_smoothness, float adt_eps,
+                                                 float shortcut_scale, int B, int L, int H, int D, int N,
+                                                 int C, int pos0, int dtype, int flags, void* stream) {
+    constexpr int kMaxDevices = 64;
+    static void* scratch_of_device[kMaxDevices] = {nullptr};
+    if (B <= 0 || L <= 0) {   // nothing to do, but still validate like the allocating entry point
+        return cdssm_b200_scan_fused_fwd(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state,
+                                         tail_state, nullptr, 0, gating_c, omega_thresh, adt_delta,
+                                         adt_smoothness, adt_eps, shortcut_scale, B, L, H, D, N, C, pos0,
+                                         dtype, flags, stream);
+    }
+    const size_t need = cdssm_b200_scan_fused_workspace_bytes(B, L, H, D, N, C);
+    if (need == 0) return CDSSM_ERR_BAD_ARG;
+    if (need > kNoAllocScratchBytes) return CDSSM_ERR_WORKSPACE;   // beyond the built-in scratch
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return CDSSM_ERR_UNSUPPORTED;
+    if (scratch_of_device[dev] == nullptr) {
+        // one-time set-up for this device (do it before any stream capture begins)
+        void* p = nullptr;
+        if (int rc = check_cuda(cudaGetSymbolAddress(&p, g_noalloc_scratch))) return rc;
+        scratch_of_device[dev] = p;
+    }
+    // Nothing in the scratch has to start at zero except the status word, which the scan itself
+    // clears on the stream; gamma/state slots are all written by the local pass before they are read.
+    return cdssm_b200_scan_fused_fwd(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state,
+                                     tail_state, scratch_of_device[dev], kNoAllocScratchBytes, gating_c,
+                                     omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, L,
+                                     H, D, N, C, pos0, dtype, flags, stream);
+}

@@ -123,6 +123,31 @@ CDSSM_API int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void
                               float shortcut_scale, int B, int L, int H, int D, int N, int C,
                               int pos0, int dtype, int flags, void* stream);
 
+/* The fused scan for callers that cannot allocate device memory (a server whose pool already owns
+ * the whole GPU, a plugin barred from the CUDA allocator, code that must not trigger the
+ * device-wide synchronisation of cudaMalloc).  Same arguments and results as
+ * cdssm_b200_scan_fused_fwd without the workspace: the scratch is a 16 MiB array built into the
+ * library (cdssm_b200_scan_fused_noalloc_max_bytes()), resident on every GPU that loads it.
+ *  - Sizes whose cdssm_b200_scan_fused_workspace_bytes exceeds that limit are refused with
+ *    CDSSM_ERR_WORKSPACE; nothing is launched.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - No cudaMalloc, cudaFree or other allocating routine is called.
+ *  - All calls on a device share the one array and it keeps what the last call left in it; the
+ *    scan clears the only word that must start at zero.  Two calls that overlap on the GPU (different
+ *    streams, no ordering between them) race on the scratch: serialise them.
+ * No counterpart in the reference (its launchers allocate their outputs themselves, e.g.
+ * intra_chunk_scan.cu:588-590). */
+CDSSM_API int cdssm_b200_scan_fused_fwd_noalloc(const void* q, const void* k, const void* v,
+                                                const void* gate_raw, const float* log_dt_scale,
+                                                const float* rope_freqs, const float* h0, void* y,
+                                                float* final_state, float* tail_state, float gating_c,
+                                                float omega_thresh, float adt_delta, float adt_smoothness,
+                                                float adt_eps, float shortcut_scale, int B, int L, int H,
+                                                int D, int N, int C, int pos0, int dtype, int flags,
+                                                void* stream);
+CDSSM_API size_t cdssm_b200_scan_fused_noalloc_max_bytes(void);
+
 /* Reads back the status word a cdssm_b200_scan_fused_fwd call left at the start of its workspace
  * (synchronises `stream`).  *status_host = 0 and CDSSM_OK if every bounded device-side wait of the
  * tensor-core kernel completed; otherwise the code of the wait that ran out and
