@@ -23,6 +23,8 @@ WORKLOADS = {  # the scan-kernel sweep: bf16 q/k/v, fp32 state, seed 2
     "cfg2_L16384": dict(B=16, H=32, D=128, N=2, C=128, L=16384, seed=2),
     "cfg2_L65536": dict(B=16, H=32, D=128, N=2, C=128, L=65536, seed=2),
     "cfg0": dict(B=2, H=4, D=64, N=2, C=64, L=512, seed=0),
+    # long-context: one sequence per head, split into contiguous segments (over GPUs and within one)
+    "cfg4_L1M": dict(B=1, H=32, D=128, N=2, C=128, L=1 << 20, seed=4, seq_parallel=True, segments=16),
 }
 DEFAULT_WORKLOAD = "cfg2_L65536"
 
@@ -198,6 +200,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--segments", type=int, default=0, help="cfg4: segments per sequence over all GPUs (default: the workload's)")
     ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (2 = the single-pass tcgen05/TMA kernel)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -222,22 +225,37 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    if w["B"] % world:
-        raise SystemExit(f"batch {w['B']} does not split over {world} ranks")
-    Bl = w["B"] // world
-    mine = range(rank * Bl, (rank + 1) * Bl)          # contiguous batch shard, no data-path collective
     dt = torch.bfloat16
-    parts = [make_batch_slice(w, b, dev, dt) for b in mine]
-    q, k, v, gate = (torch.stack([p[i] for p in parts]) for i in range(4))
+    H, N, C, L, D = w["H"], w["N"], w["C"], w["L"], w["D"]
+    seq_par = bool(w.get("seq_parallel"))
+    nseg = max(1, (args.segments or w.get("segments", 1)) // world)   # segments per rank
+    if seq_par:
+        # rank r holds tokens [r*L/world, (r+1)*L/world) of every sequence; the data are drawn in 8
+        # fixed pieces so that they do not depend on the number of GPUs
+        pieces = 8
+        if pieces % world:
+            raise SystemExit(f"{pieces} sequence pieces do not split over {world} ranks")
+        wp = dict(w, L=L // pieces)
+        parts = [make_batch_slice(wp, 1000 + i, dev, dt) for i in range(rank * pieces // world, (rank + 1) * pieces // world)]
+        q, k, v, gate = (torch.cat([p[i] for p in parts], 0).unsqueeze(0).contiguous() for i in range(4))
+        Bl, Ll = 1, L // world
+    else:
+        if w["B"] % world:
+            raise SystemExit(f"batch {w['B']} does not split over {world} ranks")
+        Bl, Ll = w["B"] // world, L
+        mine = range(rank * Bl, (rank + 1) * Bl)      # contiguous batch shard, no data-path collective
+        parts = [make_batch_slice(w, b, dev, dt) for b in mine]
+        q, k, v, gate = (torch.stack([p[i] for p in parts]) for i in range(4))
     del parts
     _, _, lds = head_params(w)
     lds = lds.to(dev)
-    H, N, C, L, D = w["H"], w["N"], w["C"], w["L"], w["D"]
     rope = (1.0 / (float(L) ** (torch.arange(H, dtype=torch.float32) / H))).to(dev)
     consts = consts_for(w)
-    y = torch.empty(Bl, L, H, N, dtype=dt, device=dev)
+    y = torch.empty(Bl, Ll, H, N, dtype=dt, device=dev)
 
     def step():
+        if seq_par:
+            return ops.scan_fused_long(q, k, v, gate, lds, rope, *consts, H, N, C, segments=nseg, flags=args.flags)
         return ops.scan_fused(q, k, v, gate, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
 
     def sync_all():
@@ -281,7 +299,11 @@ def main():
                 dk.copy_(hk, non_blocking=True)
                 dv.copy_(hv, non_blocking=True)
                 dg.copy_(hg, non_blocking=True)
-                out, _ = ops.scan_fused(dq, dk, dv, dg, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
+                if seq_par:
+                    out, _ = ops.scan_fused_long(dq, dk, dv, dg, lds, rope, *consts, H, N, C,
+                                                 segments=nseg, flags=args.flags)
+                else:
+                    out, _ = ops.scan_fused(dq, dk, dv, dg, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
                 hy.copy_(out, non_blocking=True)
 
             e2e_steps = max(2, min(args.steps, 5))
@@ -292,9 +314,25 @@ def main():
             e2e = {"value": w["B"] * L / (e2e_ms / e2e_steps / 1e3), "unit": "tokens/s",
                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                    "ms_per_step": e2e_ms / e2e_steps}
+        extra = {}
+        if seq_par:
+            tm = {}
+            ops.scan_fused_long(q, k, v, gate, lds, rope, *consts, H, N, C,
+                                segments=nseg, flags=args.flags, timings=tm)
+            t3 = torch.tensor([tm["summary_ms"], tm["handoff_ms"], tm["scan_ms"]], device=dev)
+            if dist is not None:
+                dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+            extra["segment_passes_ms"] = {"summary": float(t3[0]), "exposed_handoff": float(t3[1]), "scan": float(t3[2])}
+        elif not (args.flags & 2):
+            # the dominant kernel alone: the output pass = whole step minus (local pass + carry pass)
+            def summary_step():
+                return ops.scan_summary(k, v, gate, lds, rope, *consts, H, N, C)
+            summary_step()
+            extra["summary_ms"] = timed(summary_step, args.steps) / args.steps
         t_end = time.time()
     ms_step = ms_total / args.steps
     tokens = w["B"] * L
+    scaling = "strong"
     if rank == 0:
         peak, peak_kind = peaks()
         abytes = algorithmic_bytes(w) / world                       # per GPU per step
@@ -310,6 +348,17 @@ def main():
                              "kernel": ("scan_tc_kernel (single pass)" if args.flags & 2 else
                                         "the whole step (scan_walk local pass + scan_carry + scan_walk output pass)"),
                              "algorithmic_bytes_per_launch": abytes}}
+        if "summary_ms" in extra:
+            out_ms = ms_step - extra["summary_ms"]
+            line["roofline"]["dominant_kernel"] = {
+                "name": "scan_walk_kernel<bf16,16,true> (output pass)", "ms": out_ms,
+                "achieved": abytes / (out_ms / 1e3) / 1e9, "frac": abytes / (out_ms / 1e3) / 1e9 / peak,
+                "how": "step time minus the time of local pass + carry pass (scan_summary), both CUDA-event timed"}
+            line["roofline"]["traffic"] = 1.55 * abytes
+            line["roofline"]["traffic_how"] = ("dram bytes read+written per step from an ncu capture of cfg2_L4096 "
+                                               "(profiles/scan_walk_simt_cfg2_L4096.md), scaled by tokens")
+        if "segment_passes_ms" in extra:
+            line["segment_passes_ms"] = extra["segment_passes_ms"]
         if not args.no_cpu_baseline and world == 1:
             tps, dt_s, s, _ = run_cpu_oracle(w, 5, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",

@@ -34,6 +34,8 @@ SIGNATURES = {
     "cdssm_b200_conv1d_silu_fwd": (_I, [_P] * 4 + [_I] * 4 + [_P]),
     "cdssm_b200_scan_fused_workspace_bytes": (_c_size_t, [_I] * 6),
     "cdssm_b200_scan_fused_fwd": (_I, [_P] * 11 + [_c_size_t] + [_F] * 6 + [_I] * 9 + [_P]),
+    "cdssm_b200_scan_summary_fwd": (_I, [_P] * 9 + [_c_size_t] + [_F] * 5 + [_I] * 9 + [_P]),
+    "cdssm_b200_scan_fused_segmented_fwd": (_I, [_P] * 10 + [_c_size_t] + [_F] * 6 + [_I] * 10 + [_P]),
     "cdssm_b200_scan_fused_fwd_noalloc": (_I, [_P] * 10 + [_F] * 6 + [_I] * 9 + [_P]),
     "cdssm_b200_scan_fused_noalloc_max_bytes": (_c_size_t, []),
     "cdssm_b200_scan_fused_status": (_I, [_P, _P, _P]),

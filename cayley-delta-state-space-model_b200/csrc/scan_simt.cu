@@ -106,6 +106,10 @@ struct ScanArgs {
     const float *log_dt_scale, *rope_freqs, *h0;
     void* y;
     float *final_state, *tail_state;
+    float* total_decay;   // (B,H,N) or NULL: product over the chunks of the (rounded) chunk decays
+    int segs;             // batch rows are `segs` consecutive segments of longer sequences
+    int run_local;        // 0: the workspace already holds this input's local pass
+    int publish;          // 0: summary only, the carry pass leaves the local results in place
     float* ws_gamma;   // (B,NC,H,NP,2)
     float* ws_state;   // (B,NC,H,NP,2,D): z_{C-1} after the local pass, s_c after the carry pass
     DynConsts dc;
@@ -141,7 +145,7 @@ __device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& 
             const long long bl = (long long)b * a.L + l;
             const T* gr = gate + bl * (long long)((a.N + 5) * H);
             const T* s5 = gr + a.N * H;
-            const float pos = (float)(l + a.pos0);
+            const float pos = (float)(l + a.pos0 + (b % a.segs) * a.L);
             DynShared ds = dyn_shared<IO<T>::kBf16>(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd),
                                       IO<T>::ld(s5 + hd), IO<T>::ld(s5 + H + hd),
                                       IO<T>::ld(s5 + 2 * H + hd), IO<T>::ld(s5 + 3 * H + hd),
@@ -353,7 +357,7 @@ scan_carry_kernel(const ScanArgs a) {
     const int hd = (int)((idx / ((long long)D * NH)) % H);
     const int b = (int)(idx / ((long long)D * NH * H));
     const long long so = (((long long)b * H + hd) * a.N + 2 * j) * D + d;
-    float sr = 0.f, si = 0.f;
+    float sr = 0.f, si = 0.f, dr = 1.f, di = 0.f;
     if (a.h0) { sr = a.h0[so]; si = a.h0[so + D]; }
     const long long cstride = (long long)H * NH;            // units per chunk index
     const long long u0 = ((long long)b * NC * H + hd) * NH + j;
@@ -374,16 +378,26 @@ scan_carry_kernel(const ScanArgs a) {
         for (int i = 0; i < kBatch; i++) {
             if (c0 + i < NC) {
                 const long long u = u0 + (long long)(c0 + i) * cstride;
-                a.ws_state[u * 2 * D + d] = IO<T>::rnd(sr);       // chunk_states store
-                a.ws_state[u * 2 * D + D + d] = IO<T>::rnd(si);
+                if (a.publish) {
+                    a.ws_state[u * 2 * D + d] = IO<T>::rnd(sr);       // chunk_states store
+                    a.ws_state[u * 2 * D + D + d] = IO<T>::rnd(si);
+                }
                 const float nr = gr[i] * sr - gi[i] * si + lr[i];
                 const float ni = gr[i] * si + gi[i] * sr + li[i];
                 sr = nr;
                 si = ni;
+                const float pr = gr[i] * dr - gi[i] * di, pi = gr[i] * di + gi[i] * dr;
+                dr = pr;
+                di = pi;
             }
         }
     }
     if (a.final_state) { a.final_state[so] = sr; a.final_state[so + D] = si; }
+    if (a.total_decay && d == 0) {
+        float* td = a.total_decay + ((long long)b * H + hd) * a.N + 2 * j;
+        td[0] = dr;
+        td[1] = di;
+    }
 }
 
 template <typename T, int kCols>
@@ -398,11 +412,14 @@ static int launch_simt(const ScanArgs& a, cudaStream_t st) {
             return rc;
     }
     const unsigned blocks = (unsigned)((a.units + kUnitsPerBlock - 1) / kUnitsPerBlock);
-    scan_walk_kernel<T, kCols, false><<<blocks, kSimtThreads, smem, st>>>(a);
-    if (int rc = check_launch()) return rc;
+    if (a.run_local) {
+        scan_walk_kernel<T, kCols, false><<<blocks, kSimtThreads, smem, st>>>(a);
+        if (int rc = check_launch()) return rc;
+    }
     const long long th = (long long)a.B * a.H * (a.N / 2) * a.D;
     scan_carry_kernel<T><<<(unsigned)((th + 127) / 128), 128, 0, st>>>(a);
     if (int rc = check_launch()) return rc;
+    if (a.y == nullptr) return CDSSM_OK;   // summary only: carry out and decay product
     scan_walk_kernel<T, kCols, true><<<blocks, kSimtThreads, smem, st>>>(a);
     return check_launch();
 }
@@ -551,7 +568,8 @@ namespace cdssm {   // scan_tc.cu
 bool scan_tc_supported(int D, int N, int C, int dtype);
 int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_raw, const float* log_dt_scale,
                   const float* rope_freqs, const float* h0, void* y, float* final_state, int* status,
-                  const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, cudaStream_t st);
+                  const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
+                  cudaStream_t st);
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -572,16 +590,17 @@ extern "C" int cdssm_b200_scan_fused_status(const void* workspace, int* status_h
     return *status_host == 0 ? CDSSM_OK : CDSSM_ERR_TIMEOUT;
 }
 
-extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void* v,
-                                         const void* gate_raw, const float* log_dt_scale,
-                                         const float* rope_freqs, const float* h0, void* y,
-                                         float* final_state, float* tail_state, void* workspace,
-                                         size_t workspace_bytes, float gating_c,
-                                         float omega_thresh, float adt_delta, float adt_smoothness,
-                                         float adt_eps, float shortcut_scale, int B, int L, int H,
-                                         int D, int N, int C, int pos0, int dtype, int flags,
-                                         void* stream) {
-    if (!q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y) return CDSSM_ERR_BAD_ARG;
+static int scan_fused_impl(const void* q, const void* k, const void* v, const void* gate_raw,
+                           const float* log_dt_scale, const float* rope_freqs, const float* h0, void* y,
+                           float* final_state, float* tail_state, float* total_decay, bool summary_only,
+                           void* workspace, size_t workspace_bytes, float gating_c, float omega_thresh,
+                           float adt_delta, float adt_smoothness, float adt_eps, float shortcut_scale,
+                           int B, int L, int H, int D, int N, int C, int pos0, int segs, int dtype,
+                           int flags, void* stream) {
+    if (summary_only) { q = k; y = nullptr; tail_state = nullptr; }
+    if (!q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || (!y && !summary_only))
+        return CDSSM_ERR_BAD_ARG;
+    if (segs < 1 || (B > 0 && B % segs)) return CDSSM_ERR_BAD_ARG;
     if (B < 0 || L < 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1) || C <= 0) return CDSSM_ERR_BAD_ARG;
     if (dtype != CDSSM_BF16 && dtype != CDSSM_F32) return CDSSM_ERR_BAD_ARG;
     if (((uintptr_t)q | (uintptr_t)k) & 15) return CDSSM_ERR_BAD_ARG;   // 16-byte row loads
@@ -593,19 +612,21 @@ extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const voi
     int* status = static_cast<int*>(workspace);
     // The tensor-core kernel is selected explicitly: as measured on B200 it is still slower than
     // the CUDA-core kernels at the benchmark sizes (one sequential chain per CTA leaves the SM idle).
-    if ((flags & CDSSM_SCAN_TENSOR_CORE) && !(flags & CDSSM_SCAN_FORCE_SIMT)) {
+    if ((flags & CDSSM_SCAN_TENSOR_CORE) && !(flags & CDSSM_SCAN_FORCE_SIMT) && !summary_only) {
         if (tail_state != nullptr || !scan_tc_supported(D, N, C, dtype)) return CDSSM_ERR_UNSUPPORTED;
-    }
-    if ((flags & CDSSM_SCAN_TENSOR_CORE) && !(flags & CDSSM_SCAN_FORCE_SIMT))
         return scan_fused_tc(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state, status,
                              DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps},
-                             shortcut_scale, B, L, H, pos0, (cudaStream_t)stream);
+                             shortcut_scale, B, L, H, pos0, segs, (cudaStream_t)stream);
+    }
     if (int rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(int), (cudaStream_t)stream))) return rc;
     workspace = static_cast<char*>(workspace) + 256;
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.h0 = h0;
     a.y = y; a.final_state = final_state; a.tail_state = tail_state;
+    a.total_decay = total_decay; a.segs = segs;
+    a.run_local = (flags & CDSSM_SCAN_REUSE_LOCAL) ? 0 : 1;
+    a.publish = summary_only ? 0 : 1;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
     a.shortcut_scale = shortcut_scale;
     a.B = B; a.L = L; a.H = H; a.D = D; a.N = N; a.C = C; a.pos0 = pos0;
@@ -642,6 +663,51 @@ extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k
     if (dtype == CDSSM_BF16)
         return cols <= 8 ? launch_decode<__nv_bfloat16, 8>(a, st) : launch_decode<__nv_bfloat16, 16>(a, st);
     return cols <= 8 ? launch_decode<float, 8>(a, st) : launch_decode<float, 16>(a, st);
+}
+
+extern "C" int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void* v,
+                                         const void* gate_raw, const float* log_dt_scale,
+                                         const float* rope_freqs, const float* h0, void* y,
+                                         float* final_state, float* tail_state, void* workspace,
+                                         size_t workspace_bytes, float gating_c,
+                                         float omega_thresh, float adt_delta, float adt_smoothness,
+                                         float adt_eps, float shortcut_scale, int B, int L, int H,
+                                         int D, int N, int C, int pos0, int dtype, int flags,
+                                         void* stream) {
+    return scan_fused_impl(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state, tail_state,
+                           nullptr, false, workspace, workspace_bytes, gating_c, omega_thresh, adt_delta,
+                           adt_smoothness, adt_eps, shortcut_scale, B, L, H, D, N, C, pos0, 1, dtype, flags,
+                           stream);
+}
+
+extern "C" int cdssm_b200_scan_fused_segmented_fwd(const void* q, const void* k, const void* v,
+                                                   const void* gate_raw, const float* log_dt_scale,
+                                                   const float* rope_freqs, const float* h0, void* y,
+                                                   float* final_state, void* workspace,
+                                                   size_t workspace_bytes, float gating_c,
+                                                   float omega_thresh, float adt_delta,
+                                                   float adt_smoothness, float adt_eps,
+                                                   float shortcut_scale, int B, int L, int H, int D, int N,
+                                                   int C, int pos0, int segs, int dtype, int flags,
+                                                   void* stream) {
+    return scan_fused_impl(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state, nullptr,
+                           nullptr, false, workspace, workspace_bytes, gating_c, omega_thresh, adt_delta,
+                           adt_smoothness, adt_eps, shortcut_scale, B, L, H, D, N, C, pos0, segs, dtype,
+                           flags, stream);
+}
+
+extern "C" int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const void* gate_raw,
+                                           const float* log_dt_scale, const float* rope_freqs,
+                                           const float* h0, float* carry_out, float* total_decay,
+                                           void* workspace, size_t workspace_bytes, float gating_c,
+                                           float omega_thresh, float adt_delta, float adt_smoothness,
+                                           float adt_eps, int B, int L, int H, int D, int N, int C, int pos0,
+                                           int segs, int dtype, void* stream) {
+    if (!carry_out || !total_decay) return CDSSM_ERR_BAD_ARG;
+    return scan_fused_impl(nullptr, k, v, gate_raw, log_dt_scale, rope_freqs, h0, nullptr, carry_out,
+                           nullptr, total_decay, true, workspace, workspace_bytes, gating_c, omega_thresh,
+                           adt_delta, adt_smoothness, adt_eps, 0.f, B, L, H, D, N, C, pos0, segs, dtype,
+                           CDSSM_SCAN_FORCE_SIMT, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -63,7 +63,7 @@ struct TcArgs {
     long long* trace;             // optional: per-phase clock64 stamps of CTA 0 (performance debugging)
     DynConsts dc;
     float shortcut_scale;
-    int B, L, H, NC, pos0;
+    int B, L, H, NC, pos0, segs;
 };
 
 struct cplx { float r, i; };
@@ -246,7 +246,7 @@ __device__ __forceinline__ bool tc_prologue(TcSmem& sm, const TcArgs& a, int b, 
     if (x.valid) {
         const size_t bl = (size_t)b * L + l;
         const T* gr = a.gate_raw + bl * (size_t)(7 * H);
-        const float pos = (float)(l + a.pos0);
+        const float pos = (float)(l + a.pos0 + (b % a.segs) * L);
         DynShared ds = dyn_shared<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), IO<T>::ld(gr + 2 * H + hd),
                                         IO<T>::ld(gr + 3 * H + hd), IO<T>::ld(gr + 4 * H + hd),
                                         IO<T>::ld(gr + 5 * H + hd), IO<T>::ld(gr + 6 * H + hd), lds, freq, pos, a.dc);
@@ -600,7 +600,8 @@ bool scan_tc_supported(int D, int N, int C, int dtype) {
 // status: one int in device memory, zeroed here on the stream before the launch.
 int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_raw, const float* log_dt_scale,
                   const float* rope_freqs, const float* h0, void* y, float* final_state, int* status,
-                  const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, cudaStream_t st) {
+                  const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
+                  cudaStream_t st) {
     CUtensorMap tmK, tmQ;
     if (!make_tile_map(&tmK, k, B, L, H) || !make_tile_map(&tmQ, q, B, L, H)) return CDSSM_ERR_CUDA;
     const size_t smem = sizeof(TcSmem) + 1024;
@@ -618,7 +619,7 @@ int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_
     a.y = static_cast<__nv_bfloat16*>(y);
     a.final_state = final_state; a.status = status; a.trace = g_trace;
     a.dc = dc; a.shortcut_scale = shortcut_scale;
-    a.B = B; a.L = L; a.H = H; a.NC = (L + kTcC - 1) / kTcC; a.pos0 = pos0;
+    a.B = B; a.L = L; a.H = H; a.NC = (L + kTcC - 1) / kTcC; a.pos0 = pos0; a.segs = segs;
     scan_tc_kernel<<<B * H, kTcThreads, smem, st>>>(tmK, tmQ, a);
     return check_launch();
 }

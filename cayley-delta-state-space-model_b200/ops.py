@@ -21,7 +21,8 @@ from ._lib import CdssmError, check
 
 __all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
            "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
-           "scan_fused_workspace_bytes", "scan_fused_status", "CdssmError"]
+           "scan_fused_workspace_bytes", "scan_fused_status", "scan_summary", "scan_fused_long",
+           "CdssmError"]
 
 _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
 
@@ -196,6 +197,7 @@ class ExactCorrectionFn(Function):
 # ------------------------------------------------------------------------------------------
 FORCE_SIMT = 1
 TENSOR_CORE = 2
+REUSE_LOCAL = 8
 
 _workspaces = {}
 
@@ -219,7 +221,7 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
                rope_freqs: Tensor, gating_c: float, omega_thresh: float, adt_delta: float,
                adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int,
                chunk_size: int, h0: Tensor = None, *, shortcut_scale: float = 0.0, pos0: int = 0,
-               return_tail_state: bool = False, flags: int = 0, out: Tensor = None):
+               return_tail_state: bool = False, flags: int = 0, out: Tensor = None, segs: int = 1):
     """The scan path of one CD-SSM block in a single call.
 
     Equals, in the reference (cdssm/models/block.py:181-211): DynamicsFusedFn -> NormalizeKQFn
@@ -229,6 +231,8 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
 
     q, k: (B,L,H,D) un-normalised; v: (B,L,H,N) before the vp scale; gate_raw: (B,L,(N+5)H);
     log_dt_scale, rope_freqs: (H).  h0: optional (B,H,N,D) float32 carry into the first chunk.
+    segs > 1: the batch rows are ``segs`` consecutive segments of B/segs longer sequences (row b
+    starts at position pos0 + (b % segs) * L); see :func:`scan_fused_long`.
     Returns (y (B,L,H,N), final_state (B,H,N,D) float32[, tail_state]); final_state is the carry
     after the last chunk (feed it as h0 of the next chunk-aligned segment together with pos0);
     tail_state is the recurrent state after the last token (what decode_step continues from).
@@ -260,10 +264,18 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
         return (y, final, tail) if return_tail_state else (y, final)
     with torch.cuda.device(dev):
         ws_ptr, ws_bytes = _workspace(dev, scan_fused_workspace_bytes(B, L, H, D, N, C))
-        check(_lib.lib().cdssm_b200_scan_fused_fwd(
-            _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(y), _p(final), _p(tail), ws_ptr,
-            ws_bytes, gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale,
-            B, L, H, D, N, C, int(pos0), _dtype_code(q), int(flags), _stream()), "scan_fused_fwd")
+        if segs == 1:
+            check(_lib.lib().cdssm_b200_scan_fused_fwd(
+                _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(y), _p(final), _p(tail), ws_ptr,
+                ws_bytes, gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale,
+                B, L, H, D, N, C, int(pos0), _dtype_code(q), int(flags), _stream()), "scan_fused_fwd")
+        else:
+            if return_tail_state:
+                raise CdssmError("tail_state is not available for segmented batches")
+            check(_lib.lib().cdssm_b200_scan_fused_segmented_fwd(
+                _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(y), _p(final), ws_ptr, ws_bytes,
+                gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, L, H, D, N,
+                C, int(pos0), int(segs), _dtype_code(q), int(flags), _stream()), "scan_fused_segmented_fwd")
     return (y, final, tail) if return_tail_state else (y, final)
 
 
@@ -316,3 +328,90 @@ def scan_fused_status(device=None) -> int:
     if rc not in (0, -5):
         check(rc, "scan_fused_status")
     return out.value
+
+
+def scan_summary(k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor, rope_freqs: Tensor,
+                 gating_c: float, omega_thresh: float, adt_delta: float, adt_smoothness: float,
+                 adt_eps: float, n_heads: int, state_dim: int, chunk_size: int, h0: Tensor = None, *,
+                 pos0: int = 0, segs: int = 1):
+    """Summary of chunk-aligned segments: (carry_out (B,H,N,D), total_decay (B,H,N)) float32, the
+    carry after the last chunk for carry-in h0 and the product of the chunk decays.  Reads k, v and
+    the gates only (about half of the scan's bytes)."""
+    k = _prep(k, name="k")
+    v = _prep(v, dtype=k.dtype, name="v")
+    g = _prep(gate_raw, dtype=k.dtype, name="gate_raw")
+    B, L, H, D = k.shape
+    N, C = int(state_dim), int(chunk_size)
+    lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
+    if h0 is not None:
+        h0 = _prep(h0, dtype=torch.float32, name="h0")
+    carry = torch.zeros(B, H, N, D, dtype=torch.float32, device=k.device)
+    decay = torch.zeros(B, H, N, dtype=torch.float32, device=k.device)
+    decay[..., 0::2] = 1.0
+    if B * L == 0:
+        return (carry if h0 is None else h0.clone()), decay
+    with torch.cuda.device(k.device):
+        ws_ptr, ws_bytes = _workspace(k.device, scan_fused_workspace_bytes(B, L, H, D, N, C))
+        check(_lib.lib().cdssm_b200_scan_summary_fwd(
+            _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(carry), _p(decay), ws_ptr, ws_bytes, gating_c,
+            omega_thresh, adt_delta, adt_smoothness, adt_eps, B, L, H, D, N, C, int(pos0), int(segs),
+            _dtype_code(k), _stream()), "scan_summary_fwd")
+    return carry, decay
+
+
+def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor,
+                    rope_freqs: Tensor, gating_c: float, omega_thresh: float, adt_delta: float,
+                    adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int, chunk_size: int,
+                    h0: Tensor = None, *, segments: int = 1, group=None, shortcut_scale: float = 0.0,
+                    pos0: int = 0, flags: int = 0, timings: dict = None):
+    """The fused scan of long sequences cut into chunk-aligned segments, on one GPU or one
+    contiguous piece per rank of ``group`` (torch.distributed; rank r holds tokens
+    [r*L, (r+1)*L) of every sequence).
+
+    Pass A summarises every segment (k, v, gates only); the ranks exchange their (decay, carry)
+    summaries with one small all-gather; the carries into all segments follow from the serial
+    composition; pass B scans all segments at once as a batch of B*segments rows.
+    Returns (y (B,L,H,N), final_state (B,H,N,D)): final_state is the carry after this rank's last
+    token (on the last rank: of the whole sequence)."""
+    from . import sharding
+    B, L, H, D = q.shape
+    N, C, S = int(state_dim), int(chunk_size), int(segments)
+    if L % (S * C):
+        raise CdssmError(f"length {L} does not split into {S} chunk-aligned segments of chunk {C}")
+    Ls = L // S
+    seg = lambda t: t.contiguous().view(B * S, Ls, *t.shape[2:])
+    consts = (gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps)
+    rank, world = 0, 1
+    if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
+        rank, world = torch.distributed.get_rank(group), torch.distributed.get_world_size(group)
+    base = pos0 + rank * L
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
+    if ev: ev[0].record()
+    carry, decay = scan_summary(seg(k), seg(v), seg(gate_raw), log_dt_scale, rope_freqs, *consts, n_heads, N, C,
+                                pos0=base, segs=S)
+    if ev: ev[1].record()
+    carry = carry.view(B, S, H, N, D).transpose(0, 1)          # (S,B,H,N,D)
+    decay = decay.view(B, S, H, N).transpose(0, 1)
+    if world > 1:
+        # this rank's piece as one summary, exchanged with the other ranks
+        _, piece_out = sharding.compose_carries(decay, carry)
+        piece_dec = decay[0]
+        for g in range(1, S):
+            piece_dec = sharding.complex_mul_pairs(decay[g], piece_dec)
+        decs, outs = sharding.exchange_summaries(piece_dec.contiguous(), piece_out.contiguous(), group)
+        ins, _ = sharding.compose_carries(decs, outs, h0)
+        h_in = ins[rank]
+    else:
+        h_in = h0
+    carry_in, final = sharding.compose_carries(decay, carry, h_in)
+    h_rows = carry_in.transpose(0, 1).contiguous().view(B * S, H, N, D)
+    if ev: ev[2].record()
+    y, _ = scan_fused(seg(q), seg(k), seg(v), seg(gate_raw), log_dt_scale, rope_freqs, *consts, n_heads, N, C,
+                      h_rows, shortcut_scale=shortcut_scale, pos0=base, segs=S,
+                      flags=flags if flags & TENSOR_CORE else flags | REUSE_LOCAL)   # pass A's local results
+    if ev:
+        ev[3].record()
+        torch.cuda.synchronize()
+        timings.update(summary_ms=ev[0].elapsed_time(ev[1]), handoff_ms=ev[1].elapsed_time(ev[2]),
+                       scan_ms=ev[2].elapsed_time(ev[3]))
+    return y.view(B, L, H, N), final

@@ -48,6 +48,14 @@ def complex_mul_rows(decay: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def complex_mul_pairs(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Element-wise product of two (..., N) tensors of re/im interleaved complex pairs."""
+    out = torch.empty_like(b)
+    out[..., 0::2] = a[..., 0::2] * b[..., 0::2] - a[..., 1::2] * b[..., 1::2]
+    out[..., 1::2] = a[..., 0::2] * b[..., 1::2] + a[..., 1::2] * b[..., 0::2]
+    return out
+
+
 def compose_carries(decay: torch.Tensor, carry_out: torch.Tensor, h0: torch.Tensor = None):
     """Carries into consecutive segments from their summaries.
 

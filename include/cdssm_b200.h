@@ -93,6 +93,8 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
 /* Flags of cdssm_b200_scan_fused_fwd. */
 #define CDSSM_SCAN_DEFAULT 0
 #define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels (the default) */
+#define CDSSM_SCAN_REUSE_LOCAL 8    /* the workspace still holds the local pass of exactly these inputs, left
+                                      by cdssm_b200_scan_summary_fwd on the same workspace: skip that pass */
 #define CDSSM_SCAN_TENSOR_CORE 2   /* use the single-pass tcgen05/TMA kernel: bf16, N = 2, D = C = 128,
                                       no tail_state; CDSSM_ERR_UNSUPPORTED for other sizes */
 
@@ -122,6 +124,39 @@ CDSSM_API int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void
                               float adt_delta, float adt_smoothness, float adt_eps,
                               float shortcut_scale, int B, int L, int H, int D, int N, int C,
                               int pos0, int dtype, int flags, void* stream);
+
+/* Sequence segments.  In the reference's semantics the carry between chunks is the diagonal-linear
+ * recurrence s <- gamma_c (*) s + l_c (cdssm/csrc/kernels/inter_chunk_scan.cu:73-83) and neither
+ * gamma_c nor l_c depends on s, so a chunk-aligned segment is summarised by (total_decay, carry_out):
+ * the product of its gamma_c and its carry-out for the given carry-in h0 (NULL = zero).  Segments of
+ * one sequence - on one GPU or one per GPU - are chained by
+ *   carry_in[g+1] = total_decay[g] (*) carry_in[g] + carry_out[g]   (carry_out taken with h0 = 0)
+ * and then scanned independently with their carry_in as h0.
+ *
+ * cdssm_b200_scan_summary_fwd: k (B,L,H,D), v (B,L,H,N), gate_raw (B,L,(N+5)H) -> carry_out
+ * (B,H,N,D) float32 and total_decay (B,H,N) float32 (re/im interleaved); reads no q, writes no y.
+ * cdssm_b200_scan_fused_segmented_fwd: cdssm_b200_scan_fused_fwd whose batch rows are `segs`
+ * consecutive segments of B/segs longer sequences: row b starts at position pos0 + (b % segs) * L.
+ * Both take the workspace of cdssm_b200_scan_fused_workspace_bytes(B, L, H, D, N, C); the summary
+ * leaves its per-chunk results there, and a following fused call on the same inputs and workspace may
+ * pass CDSSM_SCAN_REUSE_LOCAL to skip recomputing them.
+ * No reference counterpart (the reference is single-GPU and scans a sequence in one piece). */
+CDSSM_API int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const void* gate_raw,
+                                          const float* log_dt_scale, const float* rope_freqs,
+                                          const float* h0, float* carry_out, float* total_decay,
+                                          void* workspace, size_t workspace_bytes, float gating_c,
+                                          float omega_thresh, float adt_delta, float adt_smoothness,
+                                          float adt_eps, int B, int L, int H, int D, int N, int C, int pos0,
+                                          int segs, int dtype, void* stream);
+CDSSM_API int cdssm_b200_scan_fused_segmented_fwd(const void* q, const void* k, const void* v,
+                                                  const void* gate_raw, const float* log_dt_scale,
+                                                  const float* rope_freqs, const float* h0, void* y,
+                                                  float* final_state, void* workspace,
+                                                  size_t workspace_bytes, float gating_c,
+                                                  float omega_thresh, float adt_delta, float adt_smoothness,
+                                                  float adt_eps, float shortcut_scale, int B, int L, int H,
+                                                  int D, int N, int C, int pos0, int segs, int dtype,
+                                                  int flags, void* stream);
 
 /* The fused scan for callers that cannot allocate device memory (a server whose pool already owns
  * the whole GPU, a plugin barred from the CUDA allocator, code that must not trigger the

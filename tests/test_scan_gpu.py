@@ -162,3 +162,34 @@ def test_prefill_tail_state_feeds_decode(ops, orc):
                           f(inp["rope_freqs"]), *const_args(inp["consts"]), H, N, t) for t in range(T0, T0 + T1)]
     y = torch.cat([y0, torch.stack(ys, 1)], 1)
     assert rel_err(to_np(y), wy) <= FP32_TOL
+
+
+# ---------------------------------------------------------------- sequence segments
+@pytest.mark.parametrize("dtype,mask,tol", [(torch.float32, 0, 2e-5), (torch.bfloat16, 13, 2.0 ** -7)])
+@pytest.mark.parametrize("B,H,L,D,N,C,S", [(2, 3, 512, 64, 2, 64, 4), (1, 2, 1024, 128, 2, 128, 8), (1, 2, 256, 32, 4, 32, 2)])
+def test_segmented_scan_equals_unsegmented(ops, orc, dtype, mask, tol, B, H, L, D, N, C, S):
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=S, bf16=mask != 0)
+    h0 = np.random.default_rng(S).standard_normal((B, H, N, D)).astype(np.float32) * 0.3
+    d = lambda x: to_dev(x, dtype)
+    f = lambda x: to_dev(x, torch.float32)
+    args = (d(inp["q"]), d(inp["k"]), d(inp["v"]), d(inp["gate_raw"]), f(inp["log_dt_scale"]), f(inp["rope_freqs"]),
+            *const_args(inp["consts"]), H, N, C, f(h0))
+    y, fin = ops.scan_fused(*args, shortcut_scale=0.4, pos0=7)
+    ys, fs = ops.scan_fused_long(*args, segments=S, shortcut_scale=0.4, pos0=7)
+    assert rel_err(to_np(ys), to_np(y)) <= tol
+    assert rel_err(to_np(fs), to_np(fin)) <= max(tol / 8, 1e-5)
+    # the summary of the whole sequence is its carry-out and the product of the chunk decays
+    carry, decay = ops.scan_summary(*args[1:4], *args[4:6], *const_args(inp["consts"]), H, N, C, f(h0), pos0=7)
+    assert rel_err(to_np(carry), to_np(fin)) <= 1e-6
+    A, _, _, _ = orc.dynamics(inp["gate_raw"], inp["log_dt_scale"], inp["rope_freqs"], inp["consts"], H, N,
+                              pos0=7, round_bf16=mask)
+    Ac = (A[..., 0::2] + 1j * A[..., 1::2]).reshape(B, L // C, C, H, N // 2).astype(np.complex128)
+    gam = np.ones((B, H, N // 2), np.complex128)
+    for c in range(L // C):
+        g = np.prod(Ac[:, c], axis=1)
+        if mask:
+            g = orc.bf16_round(g.real.astype(np.float32)) + 1j * orc.bf16_round(g.imag.astype(np.float32))
+        gam = gam * g
+    got = to_np(decay)
+    assert np.abs(got[..., 0::2] - gam.real).max() <= 2e-2 * max(np.abs(gam).max(), 1e-6)
+    assert np.abs(got[..., 1::2] - gam.imag).max() <= 2e-2 * max(np.abs(gam).max(), 1e-6)
