@@ -24,6 +24,11 @@ WORKLOADS = {  # the scan-kernel sweep: bf16 q/k/v, fp32 state, seed 2
     "cfg2_L65536": dict(B=16, H=32, D=128, N=2, C=128, L=65536, seed=2),
     "cfg0": dict(B=2, H=4, D=64, N=2, C=64, L=512, seed=0),
     # long-context: one sequence per head, split into contiguous segments (over GPUs and within one)
+    # whole-model workloads (random-initialised LM; library GEMMs around the scan path)
+    "cfg1_prefill": dict(lm=dict(d_model=768, n_layers=12, vocab_size=32000, state_dim=2, context_length=2048),
+                         B=8, L=2048, seed=1, H=24, D=64, N=2, C=64),
+    "cfg3_decode": dict(lm=dict(d_model=2048, n_layers=24, vocab_size=32000, state_dim=2, context_length=4608),
+                        B=256, L=4096, decode_steps=512, seed=3, H=64, D=64, N=2, C=64),
     "cfg4_L1M": dict(B=1, H=32, D=128, N=2, C=128, L=1 << 20, seed=4, seq_parallel=True, segments=16),
 }
 DEFAULT_WORKLOAD = "cfg2_L65536"
@@ -190,6 +195,113 @@ def workload_config(name, w):
             "layout": "operator layout (B,L,H,.), rope_freqs = L^(-h/H), constants from context_length = L"}
 
 
+# ------------------------------------------------------------------ whole-model workloads
+def lm_arm(args, w, rank, world, local_rank):
+    """cfg1: prefill tokens/s of the 12-layer LM; cfg3: greedy decode tokens/s after a 4096-token
+    prefill.  Batch-sharded over ranks (replicas, no communication)."""
+    import torch
+    from cdssm_b200.model import CdssmConfig, CdssmLM
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = CdssmConfig(**w["lm"])
+    lm = CdssmLM(cfg, device=dev, dtype=torch.bfloat16, seed=w["seed"])
+    Bl = w["B"] // world
+    g = torch.Generator().manual_seed(w["seed"] * 7919 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (Bl, w["L"]), generator=g)
+    decode = "decode_steps" in w
+
+    def sync():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    with ClockSampler(local_rank) as clocks:
+        t_begin = time.time()
+        if not decode:
+            hids = ids.pin_memory()
+            last = torch.empty(Bl, cfg.vocab_size, dtype=torch.bfloat16).pin_memory()
+
+            def step():      # end to end: ids from pinned host memory, last-position logits back
+                d = hids.to(dev, non_blocking=True)
+                for b0 in range(0, Bl, 4):
+                    last[b0:b0 + 4].copy_(lm.forward(d[b0:b0 + 4])[:, -1], non_blocking=True)
+
+            for _ in range(args.warmup):
+                step()
+            ms_step = timed(step, args.steps) / args.steps
+            tokens, launches = w["B"] * w["L"], None
+            h2d, d2h = ids.numel() * 8 * world, last.numel() * 2 * world
+        else:
+            dids = ids.to(dev)
+            caches = []
+            for b0 in range(0, Bl, 16):             # prefill in slices: activations of 16 x 4096 tokens
+                logits, c = lm.prefill(dids[b0:b0 + 16])
+                caches.append((logits[:, -1].argmax(-1), c))
+            tok = torch.cat([c[0] for c in caches])
+            cache = {"pos": w["L"], "layers": [
+                {k: torch.cat([c[1]["layers"][i][k] for c in caches]) for k in ("state", "conv")}
+                for i in range(cfg.n_layers)]}
+            del caches
+            htok = torch.empty(Bl, dtype=torch.int64).pin_memory()
+            graph, buf = lm.make_decode_graph(cache, Bl)     # one captured decode step, replayed
+            buf.copy_(tok)
+
+            def step():      # one greedy token for every sequence; the token ids go back to the host
+                graph.replay()
+                htok.copy_(buf, non_blocking=True)
+
+            for _ in range(args.warmup):
+                step()
+            n = max(args.steps, 8)
+            ms_step = timed(step, n) / n
+            args.steps = n
+            tokens = w["B"]
+            h2d, d2h = 0, Bl * 8 * world
+        t_end = time.time()
+    if rank == 0:
+        val = tokens / (ms_step / 1e3)
+        H, N, D = cfg.n_heads, cfg.state_dim, cfg.head_dim
+        line = {"metric": "decode_tokens_per_s" if decode else "prefill_tokens_per_s", "value": val,
+                "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"{args.workload}: CD-SSM LM d_model={cfg.d_model} layers={cfg.n_layers} "
+                                       f"heads={H} (reference-derived, d_inner/64) state_dim={N} vocab={cfg.vocab_size} "
+                                       f"B={w['B']} L={w['L']}" + (f", {w['decode_steps']}-step greedy decode measured per step"
+                                                                  if decode else ", random token ids"),
+                           "l2": "weights + activations per step exceed the 126 MB L2"},
+                "clocks": clocks.summary(t_begin, t_end),
+                "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "note": "the timed step already starts from host token ids / ends with host results"},
+                "gpu_launches": args.steps * cfg.n_layers * (2 if decode else 4),
+                "roofline": None}
+        if decode:
+            per_bh = 2 * N * D * 4 + 2 * D * 2 + (3 * N + 5) * 2
+            line["decode_state_bytes_per_step"] = cfg.n_layers * w["B"] * H * per_bh / world
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------ the GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -212,6 +324,8 @@ def main():
         return
     if args.warmup < 3:
         args.warmup = 3
+    if "lm" in w:
+        return lm_arm(args, w, rank, world, local_rank)
 
     import torch
     import cdssm_b200

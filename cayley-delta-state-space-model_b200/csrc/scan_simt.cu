@@ -444,6 +444,7 @@ struct DecodeArgs {
     DynConsts dc;
     float shortcut_scale;
     int B, H, D, N, pos;
+    const int* pos_dev;   // if not NULL the position is read from device memory (graph replay)
     long long units;   // B*H*NP
 };
 
@@ -485,7 +486,7 @@ decode_step_kernel(const DecodeArgs a) {
     // dynamics (every lane of the unit computes the same scalars; dynamics_fused.cu:64-139)
     const T* gr = static_cast<const T*>(a.gate_raw) + b * (long long)((a.N + 5) * H);
     const T* s5 = gr + a.N * H;
-    const float freq = a.rope_freqs[hd], pos = (float)a.pos;
+    const float freq = a.rope_freqs[hd], pos = (float)(a.pos_dev ? *a.pos_dev : a.pos);
     DynShared ds = dyn_shared<IO<T>::kBf16>(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd), IO<T>::ld(s5 + hd),
                               IO<T>::ld(s5 + H + hd), IO<T>::ld(s5 + 2 * H + hd),
                               IO<T>::ld(s5 + 3 * H + hd), IO<T>::ld(s5 + 4 * H + hd),
@@ -638,12 +639,11 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     return scan_fused_simt(a, dtype, (cudaStream_t)stream);
 }
 
-extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k, const void* v,
-                                      const void* gate_raw, const float* log_dt_scale,
-                                      const float* rope_freqs, void* y, float gating_c,
-                                      float omega_thresh, float adt_delta, float adt_smoothness,
-                                      float adt_eps, float shortcut_scale, int B, int H, int D,
-                                      int N, int pos, int dtype, void* stream) {
+static int decode_step_impl(float* state, const void* q, const void* k, const void* v,
+                            const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
+                            void* y, float gating_c, float omega_thresh, float adt_delta,
+                            float adt_smoothness, float adt_eps, float shortcut_scale, int B, int H, int D,
+                            int N, int pos, const int* pos_dev, int dtype, void* stream) {
     if (!state || !q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y)
         return CDSSM_ERR_BAD_ARG;
     if (B < 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1)) return CDSSM_ERR_BAD_ARG;
@@ -656,7 +656,7 @@ extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.y = y;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
     a.shortcut_scale = shortcut_scale;
-    a.B = B; a.H = H; a.D = D; a.N = N; a.pos = pos;
+    a.B = B; a.H = H; a.D = D; a.N = N; a.pos = pos; a.pos_dev = pos_dev;
     a.units = (long long)B * H * (N / 2);
     const int cols = (D + kLanesPerUnit - 1) / kLanesPerUnit;
     cudaStream_t st = (cudaStream_t)stream;
@@ -763,4 +763,27 @@ extern "C" int cdssm_b200_scan_fused_fwd_noalloc(const void* q, const void* k, c
                                      tail_state, scratch_of_device[dev], kNoAllocScratchBytes, gating_c,
                                      omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, L,
                                      H, D, N, C, pos0, dtype, flags, stream);
+}
+
+extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k, const void* v,
+                                      const void* gate_raw, const float* log_dt_scale,
+                                      const float* rope_freqs, void* y, float gating_c,
+                                      float omega_thresh, float adt_delta, float adt_smoothness,
+                                      float adt_eps, float shortcut_scale, int B, int H, int D,
+                                      int N, int pos, int dtype, void* stream) {
+    return decode_step_impl(state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
+                            adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, pos, nullptr,
+                            dtype, stream);
+}
+
+extern "C" int cdssm_b200_decode_step_at(float* state, const void* q, const void* k, const void* v,
+                                         const void* gate_raw, const float* log_dt_scale,
+                                         const float* rope_freqs, void* y, float gating_c,
+                                         float omega_thresh, float adt_delta, float adt_smoothness,
+                                         float adt_eps, float shortcut_scale, int B, int H, int D, int N,
+                                         const int* pos_dev, int dtype, void* stream) {
+    if (!pos_dev) return CDSSM_ERR_BAD_ARG;
+    return decode_step_impl(state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
+                            adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, 0, pos_dev,
+                            dtype, stream);
 }

@@ -303,6 +303,15 @@ def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor
         raise CdssmError("decode_step: inconsistent shapes")
     lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
     y = out if out is not None else torch.empty(B, H, N, dtype=q.dtype, device=q.device)
+    if isinstance(pos, Tensor):      # position in device memory (int32): graph-replayable
+        if pos.dtype != torch.int32 or not pos.is_cuda:
+            raise CdssmError("a tensor position must be an int32 CUDA tensor")
+        with torch.cuda.device(q.device):
+            check(_lib.lib().cdssm_b200_decode_step_at(
+                _p(state), _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh,
+                adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, _p(pos), _dtype_code(q),
+                _stream()), "decode_step_at")
+        return y
     with torch.cuda.device(q.device):
         check(_lib.lib().cdssm_b200_decode_step(
             _p(state), _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh,

@@ -204,6 +204,16 @@ CDSSM_API int cdssm_b200_decode_step(float* state, const void* q, const void* k,
                            float shortcut_scale, int B, int H, int D, int N, int pos, int dtype,
                            void* stream);
 
+/* cdssm_b200_decode_step with the position read from device memory at run time (*pos_dev), so that
+ * one captured CUDA graph of a decode step can be replayed for every position.
+ * No reference counterpart (see cdssm_b200_decode_step). */
+CDSSM_API int cdssm_b200_decode_step_at(float* state, const void* q, const void* k, const void* v,
+                                        const void* gate_raw, const float* log_dt_scale,
+                                        const float* rope_freqs, void* y, float gating_c,
+                                        float omega_thresh, float adt_delta, float adt_smoothness,
+                                        float adt_eps, float shortcut_scale, int B, int H, int D, int N,
+                                        const int* pos_dev, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
