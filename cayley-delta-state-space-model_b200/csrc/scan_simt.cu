@@ -194,16 +194,21 @@ scan_walk_kernel(const ScanArgs a) {
     const T* qbase = static_cast<const T*>(a.q) + (((long long)b * a.L + (long long)c * C) * H + hd) * D;
     const long long rstride = (long long)H * D;
 
-    float zr[kCols], zi[kCols], rr[kCols], ri[kCols];
+    // State columns are held as pairs: every element-wise operation of the step is a packed
+    // fp32x2 instruction (Blackwell FFMA2 / FMUL2), which halves the issue slots of a kernel that
+    // is bound by instruction issue.
+    constexpr int kP = kCols / 2;
+    float2 zr[kP], zi[kP], rr[kP], ri[kP];
 #pragma unroll
-    for (int i = 0; i < kCols; i++) { zr[i] = 0.f; zi[i] = 0.f; rr[i] = 0.f; ri[i] = 0.f; }
+    for (int i = 0; i < kP; i++) { zr[i] = zi[i] = rr[i] = ri[i] = make_float2(0.f, 0.f); }
     const long long sidx = ((((long long)b * a.NC + c) * H + hd) * NH + j);
     if (kOutput) {
         const float* s = a.ws_state + sidx * 2 * D;
 #pragma unroll
-        for (int i = 0; i < kCols; i++) {
-            const int d = g * kCols + i;
-            if (d < D) { rr[i] = s[d]; ri[i] = s[D + d]; }
+        for (int i = 0; i < kP; i++) {
+            const int d = g * kCols + 2 * i;
+            if (d < D) { rr[i].x = s[d]; ri[i].x = s[D + d]; }
+            if (d + 1 < D) { rr[i].y = s[d + 1]; ri[i].y = s[D + d + 1]; }
         }
     }
     float cr = 1.f, ci = 0.f;
@@ -217,9 +222,9 @@ scan_walk_kernel(const ScanArgs a) {
     // own Lc a unit sees the zero padding of the reference (a = k = v = beta = 0, ssd.py:60-67).
     const int Lw = __reduce_max_sync(0xffffffffu, Lc);
     for (int t = 0; t < Lw; t++) {
-        float kk[kCols], qq[kCols];
-        kraw.get(kk);
-        if (kOutput) qraw.get(qq);
+        float2 kk[kP], qq[kP];
+        kraw.get(reinterpret_cast<float*>(kk));
+        if (kOutput) qraw.get(reinterpret_cast<float*>(qq));
         if (t + 1 < Lc) {
             kraw.load(kbase + (long long)(t + 1) * rstride, g, D, vec);
             if (kOutput) qraw.load(qbase + (long long)(t + 1) * rstride, g, D, vec);
@@ -234,26 +239,32 @@ scan_walk_kernel(const ScanArgs a) {
         // against the state BEFORE the update, so all reductions are issued together; the
         // post-step read-out follows from  z' = a z + Kz k  =>  z'.q = a (z.q) + Kz (k.q).
         // (The reference rounds k^ and q^ to bf16 before use; here they keep fp32 precision.)
-        float skk = 0.f, zkr = 0.f, zki = 0.f;
+        const float2 zero2 = make_float2(0.f, 0.f);
+        float2 skk2 = zero2, zkr2 = zero2, zki2 = zero2;
 #pragma unroll
-        for (int i = 0; i < kCols; i++) {
-            skk += kk[i] * kk[i];
-            zkr += zr[i] * kk[i];
-            zki += zi[i] * kk[i];
+        for (int i = 0; i < kP; i++) {
+            skk2 = __ffma2_rn(kk[i], kk[i], skk2);
+            zkr2 = __ffma2_rn(zr[i], kk[i], zkr2);
+            zki2 = __ffma2_rn(zi[i], kk[i], zki2);
         }
+        float skk = skk2.x + skk2.y, zkr = zkr2.x + zkr2.y, zki = zki2.x + zki2.y;
         float sqq = 0.f, kq = 0.f, zqr = 0.f, zqi = 0.f, rkr = 0.f, rki = 0.f, rqr = 0.f, rqi = 0.f;
         if (kOutput) {
+            float2 sqq2 = zero2, kq2 = zero2, zqr2 = zero2, zqi2 = zero2, rkr2 = zero2, rki2 = zero2,
+                   rqr2 = zero2, rqi2 = zero2;
 #pragma unroll
-            for (int i = 0; i < kCols; i++) {
-                sqq += qq[i] * qq[i];
-                kq += kk[i] * qq[i];
-                zqr += zr[i] * qq[i];
-                zqi += zi[i] * qq[i];
-                rkr += rr[i] * kk[i];
-                rki += ri[i] * kk[i];
-                rqr += rr[i] * qq[i];
-                rqi += ri[i] * qq[i];
+            for (int i = 0; i < kP; i++) {
+                sqq2 = __ffma2_rn(qq[i], qq[i], sqq2);
+                kq2 = __ffma2_rn(kk[i], qq[i], kq2);
+                zqr2 = __ffma2_rn(zr[i], qq[i], zqr2);
+                zqi2 = __ffma2_rn(zi[i], qq[i], zqi2);
+                rkr2 = __ffma2_rn(rr[i], kk[i], rkr2);
+                rki2 = __ffma2_rn(ri[i], kk[i], rki2);
+                rqr2 = __ffma2_rn(rr[i], qq[i], rqr2);
+                rqi2 = __ffma2_rn(ri[i], qq[i], rqi2);
             }
+            sqq = sqq2.x + sqq2.y; kq = kq2.x + kq2.y; zqr = zqr2.x + zqr2.y; zqi = zqi2.x + zqi2.y;
+            rkr = rkr2.x + rkr2.y; rki = rki2.x + rki2.y; rqr = rqr2.x + rqr2.y; rqi = rqi2.x + rqi2.y;
         }
         skk = group_sum(skk); zkr = group_sum(zkr); zki = group_sum(zki);
         if (kOutput) {
@@ -266,11 +277,15 @@ scan_walk_kernel(const ScanArgs a) {
         const float czr = bik2 * zkr, czi = bik2 * zki;
         const float Kzr = bik * vr - (a_re * czr - a_im * czi);
         const float Kzi = bik * vi - (a_re * czi + a_im * czr);
+        const float2 are2 = make_float2(a_re, a_re), aim2 = make_float2(a_im, a_im), nim2 = make_float2(-a_im, -a_im);
+        {
+            const float2 kzr2 = make_float2(Kzr, Kzr), kzi2 = make_float2(Kzi, Kzi);
 #pragma unroll
-        for (int i = 0; i < kCols; i++) {
-            const float x = zr[i], y = zi[i];
-            zr[i] = a_re * x - a_im * y + Kzr * kk[i];
-            zi[i] = a_re * y + a_im * x + Kzi * kk[i];
+            for (int i = 0; i < kP; i++) {
+                const float2 x = zr[i], y = zi[i];
+                zr[i] = __ffma2_rn(kzr2, kk[i], __ffma2_rn(are2, x, __fmul2_rn(nim2, y)));
+                zi[i] = __ffma2_rn(kzi2, kk[i], __ffma2_rn(are2, y, __fmul2_rn(aim2, x)));
+            }
         }
         const float ncr = a_re * cr - a_im * ci, nci = a_re * ci + a_im * cr;
         cr = ncr;
@@ -283,11 +298,12 @@ scan_walk_kernel(const ScanArgs a) {
             // r' = a (r - beta (r.k^) k^) = a r + Kr k
             const float crr = bik2 * rkr, cri = bik2 * rki;
             const float Krr = -(a_re * crr - a_im * cri), Kri = -(a_re * cri + a_im * crr);
+            const float2 krr2 = make_float2(Krr, Krr), kri2 = make_float2(Kri, Kri);
 #pragma unroll
-            for (int i = 0; i < kCols; i++) {
-                const float x = rr[i], y = ri[i];
-                rr[i] = a_re * x - a_im * y + Krr * kk[i];
-                ri[i] = a_re * y + a_im * x + Kri * kk[i];
+            for (int i = 0; i < kP; i++) {
+                const float2 x = rr[i], y = ri[i];
+                rr[i] = __ffma2_rn(krr2, kk[i], __ffma2_rn(are2, x, __fmul2_rn(nim2, y)));
+                ri[i] = __ffma2_rn(kri2, kk[i], __ffma2_rn(are2, y, __fmul2_rn(aim2, x)));
             }
             if (a.shortcut_scale != 0.f) {   // block.py:202-208: sum_d shortcut[s,d] q[d] = (q^.k^)^2 v[s]
                 const float qk = iq * ik * kq;
@@ -303,9 +319,10 @@ scan_walk_kernel(const ScanArgs a) {
             if (a.tail_state != nullptr && c * C + t == a.L - 1 && active) {
                 float* ts = a.tail_state + (((long long)b * H + hd) * a.N + 2 * j) * D;
 #pragma unroll
-                for (int i = 0; i < kCols; i++) {
-                    const int d = g * kCols + i;
-                    if (d < D) { ts[d] = zr[i] + rr[i]; ts[D + d] = zi[i] + ri[i]; }
+                for (int i = 0; i < kP; i++) {
+                    const int d = g * kCols + 2 * i;
+                    if (d < D) { ts[d] = zr[i].x + rr[i].x; ts[D + d] = zi[i].x + ri[i].x; }
+                    if (d + 1 < D) { ts[d + 1] = zr[i].y + rr[i].y; ts[D + d + 1] = zi[i].y + ri[i].y; }
                 }
             }
         }
@@ -313,7 +330,7 @@ scan_walk_kernel(const ScanArgs a) {
     if (!kOutput) {
         if (Lc < C) {   // zero padding wipes the local state and the decay product
 #pragma unroll
-            for (int i = 0; i < kCols; i++) { zr[i] = 0.f; zi[i] = 0.f; }
+            for (int i = 0; i < kP; i++) { zr[i] = zi[i] = make_float2(0.f, 0.f); }
             cr = 0.f;
             ci = 0.f;
         }
@@ -321,9 +338,10 @@ scan_walk_kernel(const ScanArgs a) {
             // the carry pass consumes these as the reference's bf16 cum_A[:, -1] / local_h[:, -1]
             float* s = a.ws_state + sidx * 2 * D;
 #pragma unroll
-            for (int i = 0; i < kCols; i++) {
-                const int d = g * kCols + i;
-                if (d < D) { s[d] = IO<T>::rnd(zr[i]); s[D + d] = IO<T>::rnd(zi[i]); }
+            for (int i = 0; i < kP; i++) {
+                const int d = g * kCols + 2 * i;
+                if (d < D) { s[d] = IO<T>::rnd(zr[i].x); s[D + d] = IO<T>::rnd(zi[i].x); }
+                if (d + 1 < D) { s[d + 1] = IO<T>::rnd(zr[i].y); s[D + d + 1] = IO<T>::rnd(zi[i].y); }
             }
             if (g == 0) {
                 a.ws_gamma[sidx * 2] = IO<T>::rnd(cr);
