@@ -28,10 +28,12 @@ constexpr int kUnitsPerBlock = 16;
 constexpr int kSimtThreads = kLanesPerUnit * kUnitsPerBlock;   // 128
 constexpr int kMaxChunk = 256;
 
-__device__ __forceinline__ float group_sum(float v) {   // sum over the 8 lanes of a unit
+template <int kLanes = 8>
+__device__ __forceinline__ float group_sum(float v) {   // sum over the kLanes (8 or 16) lanes of a unit
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
     v += __shfl_xor_sync(0xffffffffu, v, 4);
+    if (kLanes == 16) v += __shfl_xor_sync(0xffffffffu, v, 8);
     return v;
 }
 
@@ -121,8 +123,8 @@ struct ScanArgs {
 // Shared-memory staging of one chunk's per-token scalars for the 16 units of a block.
 struct ChunkScalars {
     float *a_re, *a_im, *beta, *v_re, *v_im, *sel_c;   // each [kUnitsPerBlock][C]
-    __device__ ChunkScalars(float* base, int C) {
-        const int n = kUnitsPerBlock * C;
+    __device__ ChunkScalars(float* base, int C, int units_per_block = kUnitsPerBlock) {
+        const int n = units_per_block * C;
         a_re = base; a_im = base + n; beta = base + 2 * n; v_re = base + 3 * n;
         v_im = base + 4 * n; sel_c = base + 5 * n;
     }
@@ -131,14 +133,14 @@ struct ChunkScalars {
 // Dynamics of the unit's chunk: lane g handles tokens g, g+8, ...  (dynamics_fused.cu:64-139
 // and the vp scale of block.py:194-195).  Padded positions (l >= L) get a = k = v = beta = 0
 // like the reference's zero padding (ssd.py:60-67).
-template <typename T>
+template <typename T, int kLanes>
 __device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& sm, int ul, int g,
                                                int b, int c, int hd, int j) {
     const T* gate = static_cast<const T*>(a.gate_raw);
     const T* vv = static_cast<const T*>(a.v);
     const int NH = a.N >> 1, H = a.H;
     const float lds = a.log_dt_scale[hd], freq = a.rope_freqs[hd];
-    for (int t = g; t < a.C; t += kLanesPerUnit) {
+    for (int t = g; t < a.C; t += kLanes) {
         const int l = c * a.C + t;
         float ar = 0.f, ai = 0.f, be = 0.f, vr = 0.f, vi = 0.f, sc = 0.f;
         if (l < a.L) {
@@ -169,14 +171,15 @@ __device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& 
 }
 
 // kOutput = false: local pass (z only).  kOutput = true: output pass (z, r, read-out).
-template <typename T, int kCols, bool kOutput>
-__global__ void __launch_bounds__(kSimtThreads, (kOutput && kCols == 16) ? 4 : 1)
+template <typename T, int kCols, int kLanes, bool kOutput>
+__global__ void __launch_bounds__(kSimtThreads, kOutput ? (kCols == 16 ? 4 : 6) : 1)
 scan_walk_kernel(const ScanArgs a) {
+    constexpr int kUnits = kSimtThreads / kLanes;       // units per block
     extern __shared__ float smem[];
-    ChunkScalars sm(smem, a.C);
-    const int ul = threadIdx.x / kLanesPerUnit;          // unit within the block
-    const int g = threadIdx.x % kLanesPerUnit;           // lane within the unit
-    long long u = (long long)blockIdx.x * kUnitsPerBlock + ul;
+    ChunkScalars sm(smem, a.C, kUnits);
+    const int ul = threadIdx.x / kLanes;                 // unit within the block
+    const int g = threadIdx.x % kLanes;                  // lane within the unit
+    long long u = (long long)blockIdx.x * kUnits + ul;
     const bool active = u < a.units;
     if (!active) u = a.units - 1;                        // keep the lane in the shuffles
     const int NH = a.N >> 1, D = a.D, C = a.C, H = a.H;
@@ -184,9 +187,9 @@ scan_walk_kernel(const ScanArgs a) {
     const int hd = (int)((u / NH) % H);
     const int c = (int)((u / ((long long)NH * H)) % a.NC);
     const int b = (int)(u / ((long long)NH * H * a.NC));
-    const bool vec = (D == kCols * kLanesPerUnit);       // rows are 16-byte aligned slices
+    const bool vec = (D == kCols * kLanes);              // rows are 16-byte aligned slices
 
-    stage_dynamics<T>(a, sm, ul, g, b, c, hd, j);
+    stage_dynamics<T, kLanes>(a, sm, ul, g, b, c, hd, j);
     __syncwarp();
 
     const int Lc = min(C, a.L - c * C);                  // valid tokens of this chunk
@@ -266,10 +269,10 @@ scan_walk_kernel(const ScanArgs a) {
             sqq = sqq2.x + sqq2.y; kq = kq2.x + kq2.y; zqr = zqr2.x + zqr2.y; zqi = zqi2.x + zqi2.y;
             rkr = rkr2.x + rkr2.y; rki = rki2.x + rki2.y; rqr = rqr2.x + rqr2.y; rqi = rqi2.x + rqi2.y;
         }
-        skk = group_sum(skk); zkr = group_sum(zkr); zki = group_sum(zki);
+        skk = group_sum<kLanes>(skk); zkr = group_sum<kLanes>(zkr); zki = group_sum<kLanes>(zki);
         if (kOutput) {
-            sqq = group_sum(sqq); kq = group_sum(kq); zqr = group_sum(zqr); zqi = group_sum(zqi);
-            rkr = group_sum(rkr); rki = group_sum(rki); rqr = group_sum(rqr); rqi = group_sum(rqi);
+            sqq = group_sum<kLanes>(sqq); kq = group_sum<kLanes>(kq); zqr = group_sum<kLanes>(zqr); zqi = group_sum<kLanes>(zqi);
+            rkr = group_sum<kLanes>(rkr); rki = group_sum<kLanes>(rki); rqr = group_sum<kLanes>(rqr); rqi = group_sum<kLanes>(rqi);
         }
         const float ik = rsqrtf(skk + kEps);
         const float bik = be * ik, bik2 = bik * ik;
@@ -352,7 +355,7 @@ scan_walk_kernel(const ScanArgs a) {
         __syncwarp();
         if (active) {
             T* y = static_cast<T*>(a.y);
-            for (int t = g; t < Lc; t += kLanesPerUnit) {
+            for (int t = g; t < Lc; t += kLanes) {
                 T* o = y + (((long long)b * a.L + c * C + t) * H + hd) * a.N + 2 * j;
                 IO<T>::st(o, sm.v_re[so + t]);
                 IO<T>::st(o + 1, sm.v_im[so + t]);
@@ -418,38 +421,48 @@ scan_carry_kernel(const ScanArgs a) {
     }
 }
 
-template <typename T, int kCols>
+template <typename T, int kCols, int kLanes>
 static int launch_simt(const ScanArgs& a, cudaStream_t st) {
-    const size_t smem = (size_t)6 * kUnitsPerBlock * a.C * sizeof(float);
-    if (smem > 48 * 1024) {   // opt in to more than 48 KB of dynamic shared memory (C > 128)
-        if (int rc = check_cuda(cudaFuncSetAttribute(scan_walk_kernel<T, kCols, false>,
+    constexpr int kUnits = kSimtThreads / kLanes;
+    const size_t smem = (size_t)6 * kUnits * a.C * sizeof(float);
+    if (smem > 48 * 1024) {   // opt in to more than 48 KB of dynamic shared memory
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_walk_kernel<T, kCols, kLanes, false>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
             return rc;
-        if (int rc = check_cuda(cudaFuncSetAttribute(scan_walk_kernel<T, kCols, true>,
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_walk_kernel<T, kCols, kLanes, true>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
             return rc;
     }
-    const unsigned blocks = (unsigned)((a.units + kUnitsPerBlock - 1) / kUnitsPerBlock);
+    const unsigned blocks = (unsigned)((a.units + kUnits - 1) / kUnits);
     if (a.run_local) {
-        scan_walk_kernel<T, kCols, false><<<blocks, kSimtThreads, smem, st>>>(a);
+        scan_walk_kernel<T, kCols, kLanes, false><<<blocks, kSimtThreads, smem, st>>>(a);
         if (int rc = check_launch()) return rc;
     }
     const long long th = (long long)a.B * a.H * (a.N / 2) * a.D;
     scan_carry_kernel<T><<<(unsigned)((th + 127) / 128), 128, 0, st>>>(a);
     if (int rc = check_launch()) return rc;
     if (a.y == nullptr) return CDSSM_OK;   // summary only: carry out and decay product
-    scan_walk_kernel<T, kCols, true><<<blocks, kSimtThreads, smem, st>>>(a);
+    scan_walk_kernel<T, kCols, kLanes, true><<<blocks, kSimtThreads, smem, st>>>(a);
     return check_launch();
 }
 
-int scan_fused_simt(const ScanArgs& a, int dtype, cudaStream_t st) {
+// Column split: D <= 64 -> 8 lanes x 8 columns; D <= 128 -> 8 lanes x 16 columns, or (wide) 16 lanes x 8
+// columns, which halves the state registers per thread and doubles the resident warps - measured
+// slower on B200 (10.8 ms against 8.9 ms at the benchmark size: the per-unit scalar work and the extra
+// shuffle stage cost more than the occupancy gains), so the narrow split is the one used.
+int scan_fused_simt(const ScanArgs& a, int dtype, bool wide, cudaStream_t st) {
     const int cols = (a.D + kLanesPerUnit - 1) / kLanesPerUnit;
     if (dtype == CDSSM_BF16) {
-        return cols <= 8 ? launch_simt<__nv_bfloat16, 8>(a, st) : launch_simt<__nv_bfloat16, 16>(a, st);
+        if (cols <= 8) return launch_simt<__nv_bfloat16, 8, 8>(a, st);
+        return wide ? launch_simt<__nv_bfloat16, 8, 16>(a, st) : launch_simt<__nv_bfloat16, 16, 8>(a, st);
     }
-    return cols <= 8 ? launch_simt<float, 8>(a, st) : launch_simt<float, 16>(a, st);
+    if (cols <= 8) return launch_simt<float, 8, 8>(a, st);
+    return wide ? launch_simt<float, 8, 16>(a, st) : launch_simt<float, 16, 8>(a, st);
 }
 
+}  // namespace cdssm
+
+namespace cdssm {
 // ---------------------------------------------------------------------------------------------
 // One-token decode step.  Eight lanes per (batch, head, pair): dynamics for position `pos`,
 // normalise q/k, one delta-rule step on the fp32 state in place, read-out.  One pass over the
@@ -654,7 +667,7 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     a.ws_gamma = static_cast<float*>(workspace);
     a.ws_state = reinterpret_cast<float*>(static_cast<char*>(workspace) +
                                           align256((size_t)a.units * 2 * sizeof(float)));
-    return scan_fused_simt(a, dtype, (cudaStream_t)stream);
+    return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
 }
 
 static int decode_step_impl(float* state, const void* q, const void* k, const void* v,
