@@ -128,9 +128,13 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
             if (!q_ok && mbar_test(&sm.full_q, par(c))) { q_ok = true; pend_q = false; }
             if (k_ok && q_ok && (c == 0 || mbar_test(&sm.gp1_free, par(c - 1)))) {
                 tc_fence_after();
-                for (int j = 0; j < 8; j++)
+#pragma unroll 1
+    #pragma unroll 1
+            for (int j = 0; j < 8; j++)
                     umma_bf16(tm + kColG, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
-                for (int j = 0; j < 8; j++)
+#pragma unroll 1
+    #pragma unroll 1
+            for (int j = 0; j < 8; j++)
                     umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 0), idesc_gp, j > 0);
                 umma_commit(&sm.mma_gp0);
                 if (a.trace && blockIdx.x == 0 && c < 8) a.trace[(c * 5 + 4) * 16 + 0] = clock64();
@@ -140,8 +144,10 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
         if (i_kr < i_gp0 && mbar_test(&sm.s_ready, par(i_kr))) {   // kappa = K s^T, rho = Q s^T
             const int st = i_kr & 1;
             tc_fence_after();
+#pragma unroll 1
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColKappa, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
+#pragma unroll 1
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColRho, kmaj(qaddr, kSlabBytes, j, 0), kmaj(saddr, 2048, j, 0), idesc_sk, j > 0);
             umma_commit(&sm.mma_kr);
@@ -151,8 +157,10 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
         if (i_gp1 < i_kr && mbar_test(&sm.gp0_free, par(i_gp1))) {   // pass 1: columns 64..127
             const int st = i_gp1 & 1;
             tc_fence_after();
+#pragma unroll 1
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColG, kmaj(kaddr[st], kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
+#pragma unroll 1
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColP, kmaj(qaddr, kSlabBytes, j, 0), kmaj(kaddr[st], kSlabBytes, j, 64 * 128), idesc_gp, j > 0);
             umma_commit(&sm.mma_gp1);
@@ -169,6 +177,7 @@ __device__ __forceinline__ void tc_producer(TcSmem& sm, const CUtensorMap* tmK, 
         if (i_ell < i_gp1 && mbar_test(&sm.omega_ready, par(i_ell))) {
             const int st = i_ell & 1;
             tc_fence_after();
+#pragma unroll 1
             for (int j = 0; j < 8; j++)
                 umma_bf16(tm + kColEll, umma_desc_sw128(kaddr[st] + (uint32_t)j * 2048, kSlabBytes, 1024),
                           kmaj(oaddr, 2048, j, 0), idesc_el, j > 0);
@@ -232,7 +241,7 @@ struct TokenCtx {          // per-token quantities of one chunk, produced by tc_
 // Everything of chunk c that does not depend on the carry or on tensor memory: dynamics of token t
 // (dynamics_fused.cu:64-139; vp scale of block.py:194-195), the in-block prefix / suffix products
 // of a, the block products, and |q_t|^-1 from the Q tile row.
-__device__ __forceinline__ bool tc_prologue(TcSmem& sm, const TcArgs& a, int b, int hd, int c, float lds,
+__device__ __noinline__ bool tc_prologue(TcSmem& sm, const TcArgs& a, int b, int hd, int c, float lds,
                                             float freq, TokenCtx& x) {
     using T = __nv_bfloat16;
     volatile int* ab = &sm.abort_flag;
@@ -342,66 +351,85 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
         const cplx at = x.at, vg = x.vg, W = x.W, W0 = x.W0, V = x.V;
         const float be = x.be, mt = x.mt;
         TC_STAMP(0);
-        // ---- column blocks I = 0..J
+        // ---- off-diagonal column blocks I < J.  Loops over groups of eight columns stay rolled and
+        // read tensor memory with a run-time column address: the fully unrolled form of this kernel was
+        // 110 KB of straight-line code and stalled on instruction fetch.
         cplx agw = {0, 0}, agx = {0, 0}, apw = {0, 0}, apx = {0, 0};
-        float g[32], p[32];
         bool fail = false;
-        for (int I = 0; I <= J; I++) {
+        for (int I = 0; I < J; I++) {
             if (!warp_wait(I < 2 ? &sm.mma_gp0 : &sm.mma_gp1, ph, ab)) { code = 13; fail = true; break; }
             tc_fence_after();
-            tmem_ld32x2(tlane + kColG + (I & 1) * 32, g, tlane + kColP + (I & 1) * 32, p);
-            if (I == (J < 1 ? J : 1)) {   // this warp's last read of the first column half
+            if (!warp_wait(&sm.blk_done[I], ph, ab)) { code = 14; fail = true; break; }
+            if (I > 0) {
+                const cplx bpI = I == 1 ? x.bp1 : x.bp2;
+                agw = cmul(agw, bpI); agx = cmul(agx, bpI); apw = cmul(apw, bpI); apx = cmul(apx, bpI);
+            }
+#pragma unroll 1
+            for (int grp = 0; grp < 4; grp++) {
+                float g8[8], p8[8];
+                tmem_ld8x2(tlane + kColG + (I & 1) * 32 + grp * 8, g8, tlane + kColP + (I & 1) * 32 + grp * 8, p8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float4 wx = sm.wx[I * 32 + grp * 8 + e];
+                    agw.r += g8[e] * wx.x; agw.i += g8[e] * wx.y; agx.r += g8[e] * wx.z; agx.i += g8[e] * wx.w;
+                    apw.r += p8[e] * wx.x; apw.i += p8[e] * wx.y; apx.r += p8[e] * wx.z; apx.i += p8[e] * wx.w;
+                }
+            }
+            if (I == 1 && J >= 2) {   // warps 2, 3: last read of the first column half
                 tc_fence_before();
                 __syncwarp();
                 if (tl == 0) mbar_arrive(&sm.gp0_free);
             }
-            if (I < J) {
-                if (!warp_wait(&sm.blk_done[I], ph, ab)) { code = 14; fail = true; break; }
-                if (I > 0) {
-                    const cplx bpI = I == 1 ? x.bp1 : x.bp2;
-                    agw = cmul(agw, bpI); agx = cmul(agx, bpI); apw = cmul(apw, bpI); apx = cmul(apx, bpI);
-                }
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float4 wx = sm.wx[I * 32 + i];
-                    agw.r += g[i] * wx.x; agw.i += g[i] * wx.y; agx.r += g[i] * wx.z; agx.i += g[i] * wx.w;
-                    apw.r += p[i] * wx.x; apw.i += p[i] * wx.y; apx.r += p[i] * wx.z; apx.i += p[i] * wx.w;
-                }
-            }
         }
         if (fail) break;
         TC_STAMP(2);
-        // every TMEM read of this chunk's G/P is done
-        tc_fence_before();
-        __syncwarp();
-        if (tl == 0) mbar_arrive(&sm.gp1_free);
-
-        // ---- diagonal block: g, p hold G[t, 32J..] and P[t, 32J..]
-        float gd = 0.f, pd = 0.f;
+        // ---- diagonal block J: P[t, 32J..] into registers, G[t, 32J..] streamed through phase A
+        if (!warp_wait(J < 2 ? &sm.mma_gp0 : &sm.mma_gp1, ph, ab)) { code = 13; break; }
+        tc_fence_after();
+        float p[32];
+        tmem_ld32(tlane + kColP + (J & 1) * 32, p);
+        float pd = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-            if (i == tl) { gd = g[i]; pd = p[i]; }
-        }
-        const float nt = rsqrtf(gd + kEps);                  // |k_t|^-1 from the Gram diagonal
+        for (int i = 0; i < 32; i++) pd = (i == tl) ? p[i] : pd;
         // Phase A (no dependence on other lanes): coefficients of the unit-lower-triangular system
         // for the unknowns u = n w and x~ = n x,
         //   u_t = n_t b_t - sum_{i<t} cc[i] u_i,  cc[i] = beta_t n_t^2 a_t Gamma0[t,i] G_raw[t,i],
         // Gamma0[t,i] = prod a_r, i < r <= t-1, built leftwards from the diagonal (0 for i >= t).
-        const float bnn = be * nt * nt;
-        const cplx f = {bnn * at.r, bnn * at.i};
+        // n_t = |k_t|^-1 comes from the Gram diagonal, so the scalar factor is applied afterwards.
         cplx cc[32];
+        float gd = 0.f;
         {
             cplx cur = {1.f, 0.f};
+#pragma unroll 1
+            for (int grp = 3; grp >= 0; grp--) {
+                if (grp < 3) {
 #pragma unroll
-            for (int i = 31; i >= 0; i--) {
-                const float2 ai = sm.a[ph][J * 32 + i];
-                const bool on = i < tl;
-                const cplx fg = cmul(f, cur);
-                cc[i] = {on ? fg.r * g[i] : 0.f, on ? fg.i * g[i] : 0.f};
-                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
-                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+                    for (int k = 31; k >= 8; k--) cc[k] = cc[k - 8];
+                }
+                float g8[8];
+                tmem_ld8(tlane + kColG + (J & 1) * 32 + grp * 8, g8);
+#pragma unroll
+                for (int e = 7; e >= 0; e--) {
+                    const int i = grp * 8 + e;
+                    const float2 ai = sm.a[ph][J * 32 + i];
+                    const bool on = i < tl;
+                    gd = (i == tl) ? g8[e] : gd;
+                    const cplx fg = cmul(at, cur);
+                    cc[e] = {on ? fg.r * g8[e] : 0.f, on ? fg.i * g8[e] : 0.f};
+                    const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                    cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+                }
             }
         }
+        // every TMEM read of this chunk's G/P is done
+        tc_fence_before();
+        __syncwarp();
+        if (tl == 0) {
+            if (J < 2) mbar_arrive(&sm.gp0_free);
+            mbar_arrive(&sm.gp1_free);
+        }
+        const float nt = rsqrtf(gd + kEps);                  // |k_t|^-1
+        const float bnn = be * nt * nt;
         TC_STAMP(3);
         // ---- kappa_t = k_t.s, rho_t = q_t.s (raw rows; scaled by the norms)
         if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
@@ -416,14 +444,22 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
         const cplx gk = cmul(gam, kap);
         cplx cw = {nt * be * (vg.r - nt * wagw.r), nt * be * (vg.i - nt * wagw.i)};
         cplx cx = {nt * be * (nt * gk.r - nt * wagx.r), nt * be * (nt * gk.i - nt * wagx.i)};
-        // Phase B: the sequential substitution, nothing else in the loop
+        // Phase B: the sequential substitution, eight steps per rolled iteration; the coefficient
+        // queue is rotated so that the unrolled body always reads slots 0..7.
+#pragma unroll 1
+        for (int grp = 0; grp < 4; grp++) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-            const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
-            cw.r -= cc[i].r * uw.r - cc[i].i * uw.i;
-            cw.i -= cc[i].r * uw.i + cc[i].i * uw.r;
-            cx.r -= cc[i].r * ux.r - cc[i].i * ux.i;
-            cx.i -= cc[i].r * ux.i + cc[i].i * ux.r;
+            for (int e = 0; e < 8; e++) {
+                const int i = grp * 8 + e;
+                const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+                const float cr_ = bnn * cc[e].r, ci_ = bnn * cc[e].i;
+                cw.r -= cr_ * uw.r - ci_ * uw.i;
+                cw.i -= cr_ * uw.i + ci_ * uw.r;
+                cx.r -= cr_ * ux.r - ci_ * ux.i;
+                cx.i -= cr_ * ux.i + ci_ * ux.r;
+            }
+#pragma unroll
+            for (int k = 0; k < 24; k++) cc[k] = cc[k + 8];
         }
         TC_STAMP(4);
         // ---- publish V n w, V n x for the later blocks; omega = Gamma[C-1,t] n_t w_t for l
@@ -444,22 +480,28 @@ __device__ __forceinline__ void tc_compute(TcSmem& sm, const TcArgs& a, int b, i
             mbar_arrive(&sm.omega_ready);
         }
         // Phase C (off the other warps' critical path): in-block part of the read-out,
-        // sum_{i<t} P_raw[t,i] Gamma0[t,i] (a_t u_i - x~_i)
+        // sum_{i<t} P_raw[t,i] Gamma0[t,i] (a_t u_i - x~_i); columns taken from the top of a rotating queue
         cplx yin = {0.f, 0.f};
         {
             cplx cur = {1.f, 0.f};
+#pragma unroll 1
+            for (int grp = 3; grp >= 0; grp--) {
 #pragma unroll
-            for (int i = 31; i >= 0; i--) {
-                const float2 ai = sm.a[ph][J * 32 + i];
-                const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
-                const bool on = i < tl;
-                const cplx au = cmul(at, uw);
-                const cplx e = cmul(cur, cplx{au.r - ux.r, au.i - ux.i});
-                const float pi = on ? p[i] : 0.f;
-                yin.r += pi * e.r;
-                yin.i += pi * e.i;
-                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
-                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+                for (int e = 7; e >= 0; e--) {
+                    const int i = grp * 8 + e;
+                    const float2 ai = sm.a[ph][J * 32 + i];
+                    const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+                    const bool on = i < tl;
+                    const cplx au = cmul(at, uw);
+                    const cplx ee = cmul(cur, cplx{au.r - ux.r, au.i - ux.i});
+                    const float pi = on ? p[24 + e] : 0.f;
+                    yin.r += pi * ee.r;
+                    yin.i += pi * ee.i;
+                    const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                    cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+                }
+#pragma unroll
+                for (int k = 31; k >= 8; k--) p[k] = p[k - 8];
             }
         }
         // ---- read-out: local + correction taken before the step (exact_correction.cu:90-94)

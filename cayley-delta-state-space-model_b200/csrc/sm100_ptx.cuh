@@ -198,6 +198,28 @@ __device__ __forceinline__ void tmem_ld32x2(uint32_t ta, float* ra, uint32_t tb,
         : "r"(ta), "r"(tb)
         : "memory");
 }
+// Eight columns of each of two regions, one wait (used inside rolled loops: the address is dynamic).
+__device__ __forceinline__ void tmem_ld8x2(uint32_t ta, float* ra, uint32_t tb, float* rb) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(ra);
+    uint32_t* w = reinterpret_cast<uint32_t*>(rb);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%16];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8, %9, %10, %11, %12, %13, %14, %15}, [%17];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+          "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+        : "r"(ta), "r"(tb)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t ta, float* ra) {
+    uint32_t* u = reinterpret_cast<uint32_t*>(ra);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
+        : "r"(ta)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float* r) {
     uint32_t* u = reinterpret_cast<uint32_t*>(r);
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n\t"
