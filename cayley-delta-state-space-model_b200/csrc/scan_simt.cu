@@ -364,6 +364,135 @@ scan_walk_kernel(const ScanArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// "Exact" semantics: the plain sequential recurrence over the whole sequence (what the reference's
+// chunked scan equals inside its first chunk, and what the one-token decode step continues),
+//   z_t = a_t (z_{t-1} - beta_t (z_{t-1}.k^_t) k^_t) + beta_t v_t k^_t,  y_t = sel_C (z_t.q^_t + shortcut),
+// with z_{-1} = h0.  One 8-lane unit walks one (batch, head, pair) sequence from start to end; the
+// dynamics are staged in shared memory kMaxChunk tokens at a time.  Parallel over B*H*N/2 only.
+template <typename T, int kCols>
+__global__ void __launch_bounds__(kSimtThreads)
+scan_recurrent_kernel(const ScanArgs a) {
+    constexpr int kLanes = kLanesPerUnit, kP = kCols / 2;
+    extern __shared__ float smem[];
+    const int CS = a.C;                                   // staging length (tokens per stage)
+    ChunkScalars sm(smem, CS);
+    const int ul = threadIdx.x / kLanes, g = threadIdx.x % kLanes;
+    long long u = (long long)blockIdx.x * kUnitsPerBlock + ul;
+    const bool active = u < a.units;
+    if (!active) u = a.units - 1;
+    const int NH = a.N >> 1, D = a.D, H = a.H;
+    const int j = (int)(u % NH);
+    const int hd = (int)((u / NH) % H);
+    const int b = (int)(u / ((long long)NH * H));
+    const bool vec = (D == kCols * kLanes);
+    const long long rstride = (long long)H * D;
+    float2 zr[kP], zi[kP];
+    {
+        const float* h = a.h0 ? a.h0 + (((long long)b * H + hd) * a.N + 2 * j) * D : nullptr;
+#pragma unroll
+        for (int i = 0; i < kP; i++) {
+            const int d = g * kCols + 2 * i;
+            zr[i] = make_float2(h && d < D ? h[d] : 0.f, h && d + 1 < D ? h[d + 1] : 0.f);
+            zi[i] = make_float2(h && d < D ? h[D + d] : 0.f, h && d + 1 < D ? h[D + d + 1] : 0.f);
+        }
+    }
+    const int so = ul * CS;
+    for (int c = 0; c < a.NC; c++) {
+        __syncwarp();
+        stage_dynamics<T, kLanes>(a, sm, ul, g, b, c, hd, j);
+        __syncwarp();
+        const int Lc = min(CS, a.L - c * CS);
+        const T* kbase = static_cast<const T*>(a.k) + (((long long)b * a.L + (long long)c * CS) * H + hd) * D;
+        const T* qbase = static_cast<const T*>(a.q) + (((long long)b * a.L + (long long)c * CS) * H + hd) * D;
+        RowSlice<T, kCols> kraw, qraw;
+        kraw.load(kbase, g, D, vec);
+        qraw.load(qbase, g, D, vec);
+        for (int t = 0; t < Lc; t++) {
+            float2 kk[kP], qq[kP];
+            kraw.get(reinterpret_cast<float*>(kk));
+            qraw.get(reinterpret_cast<float*>(qq));
+            if (t + 1 < Lc) {
+                kraw.load(kbase + (long long)(t + 1) * rstride, g, D, vec);
+                qraw.load(qbase + (long long)(t + 1) * rstride, g, D, vec);
+            }
+            const float a_re = sm.a_re[so + t], a_im = sm.a_im[so + t], be = sm.beta[so + t];
+            const float vr = sm.v_re[so + t], vi = sm.v_im[so + t];
+            const float2 zero2 = make_float2(0.f, 0.f);
+            float2 skk2 = zero2, sqq2 = zero2, kq2 = zero2, zkr2 = zero2, zki2 = zero2, zqr2 = zero2, zqi2 = zero2;
+#pragma unroll
+            for (int i = 0; i < kP; i++) {
+                skk2 = __ffma2_rn(kk[i], kk[i], skk2);
+                sqq2 = __ffma2_rn(qq[i], qq[i], sqq2);
+                kq2 = __ffma2_rn(kk[i], qq[i], kq2);
+                zkr2 = __ffma2_rn(zr[i], kk[i], zkr2);
+                zki2 = __ffma2_rn(zi[i], kk[i], zki2);
+                zqr2 = __ffma2_rn(zr[i], qq[i], zqr2);
+                zqi2 = __ffma2_rn(zi[i], qq[i], zqi2);
+            }
+            const float skk = group_sum(skk2.x + skk2.y), sqq = group_sum(sqq2.x + sqq2.y);
+            const float kq = group_sum(kq2.x + kq2.y);
+            const float zkr = group_sum(zkr2.x + zkr2.y), zki = group_sum(zki2.x + zki2.y);
+            const float zqr = group_sum(zqr2.x + zqr2.y), zqi = group_sum(zqi2.x + zqi2.y);
+            const float ik = rsqrtf(skk + kEps), iq = rsqrtf(sqq + kEps);
+            const float bik = be * ik, bik2 = bik * ik;
+            const float czr = bik2 * zkr, czi = bik2 * zki;
+            const float Kzr = bik * vr - (a_re * czr - a_im * czi);
+            const float Kzi = bik * vi - (a_re * czi + a_im * czr);
+            const float2 are2 = make_float2(a_re, a_re), aim2 = make_float2(a_im, a_im), nim2 = make_float2(-a_im, -a_im);
+            const float2 kzr2 = make_float2(Kzr, Kzr), kzi2 = make_float2(Kzi, Kzi);
+#pragma unroll
+            for (int i = 0; i < kP; i++) {
+                const float2 x = zr[i], y = zi[i];
+                zr[i] = __ffma2_rn(kzr2, kk[i], __ffma2_rn(are2, x, __fmul2_rn(nim2, y)));
+                zi[i] = __ffma2_rn(kzi2, kk[i], __ffma2_rn(are2, y, __fmul2_rn(aim2, x)));
+            }
+            float yr = iq * (a_re * zqr - a_im * zqi + Kzr * kq);
+            float yi = iq * (a_re * zqi + a_im * zqr + Kzi * kq);
+            if (a.shortcut_scale != 0.f) {
+                const float qk = iq * ik * kq;
+                yr += a.shortcut_scale * qk * qk * vr;
+                yi += a.shortcut_scale * qk * qk * vi;
+            }
+            if (g == 0) {
+                const float sc = sm.sel_c[so + t];
+                sm.v_re[so + t] = IO<T>::rnd(IO<T>::rnd(yr) * sc);
+                sm.v_im[so + t] = IO<T>::rnd(IO<T>::rnd(yi) * sc);
+            }
+        }
+        __syncwarp();
+        if (active) {
+            T* y = static_cast<T*>(a.y);
+            for (int t = g; t < Lc; t += kLanes) {
+                T* o = y + (((long long)b * a.L + c * CS + t) * H + hd) * a.N + 2 * j;
+                IO<T>::st(o, sm.v_re[so + t]);
+                IO<T>::st(o + 1, sm.v_im[so + t]);
+            }
+        }
+    }
+    if (active && a.final_state) {
+        float* fs = a.final_state + (((long long)b * H + hd) * a.N + 2 * j) * D;
+#pragma unroll
+        for (int i = 0; i < kP; i++) {
+            const int d = g * kCols + 2 * i;
+            if (d < D) { fs[d] = zr[i].x; fs[D + d] = zi[i].x; }
+            if (d + 1 < D) { fs[d + 1] = zr[i].y; fs[D + d + 1] = zi[i].y; }
+        }
+    }
+}
+
+template <typename T, int kCols>
+static int launch_recurrent(ScanArgs a, cudaStream_t st) {
+    a.C = a.L < 128 ? a.L : 128;                          // staging length only: no chunk semantics here
+    a.NC = (a.L + a.C - 1) / a.C;
+    a.segs = 1;
+    a.units = (long long)a.B * a.H * (a.N / 2);
+    const size_t smem = (size_t)6 * kUnitsPerBlock * a.C * sizeof(float);
+    const unsigned blocks = (unsigned)((a.units + kUnitsPerBlock - 1) / kUnitsPerBlock);
+    scan_recurrent_kernel<T, kCols><<<blocks, kSimtThreads, smem, st>>>(a);
+    return check_launch();
+}
+
 // Carry pass: s_0 = h0 (or 0); for every chunk: publish s_c, then s <- gamma_c * s + z_{C-1}.
 // One thread per (b, h, pair, d).  Chunks are taken eight at a time so that the loads of a
 // batch are in flight together (the recurrence itself is two FMAs per chunk).
@@ -652,6 +781,7 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     }
     if (int rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(int), (cudaStream_t)stream))) return rc;
     workspace = static_cast<char*>(workspace) + 256;
+    if ((flags & CDSSM_SCAN_EXACT) && (summary_only || segs != 1)) return CDSSM_ERR_UNSUPPORTED;
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.h0 = h0;
@@ -667,6 +797,20 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     a.ws_gamma = static_cast<float*>(workspace);
     a.ws_state = reinterpret_cast<float*>(static_cast<char*>(workspace) +
                                           align256((size_t)a.units * 2 * sizeof(float)));
+    if (flags & CDSSM_SCAN_EXACT) {
+        // the recurrent state after the last token is both the "carry" and the tail state
+        const int cols = (D + kLanesPerUnit - 1) / kLanesPerUnit;
+        cudaStream_t st = (cudaStream_t)stream;
+        float* extra = tail_state;
+        if (!a.final_state) { a.final_state = tail_state; extra = nullptr; }
+        int rc;
+        if (dtype == CDSSM_BF16) rc = cols <= 8 ? launch_recurrent<__nv_bfloat16, 8>(a, st) : launch_recurrent<__nv_bfloat16, 16>(a, st);
+        else rc = cols <= 8 ? launch_recurrent<float, 8>(a, st) : launch_recurrent<float, 16>(a, st);
+        if (rc == CDSSM_OK && extra && a.final_state)
+            rc = check_cuda(cudaMemcpyAsync(extra, a.final_state, sizeof(float) * (size_t)B * H * N * D,
+                                            cudaMemcpyDeviceToDevice, st));
+        return rc;
+    }
     return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
 }
 

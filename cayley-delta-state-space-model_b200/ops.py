@@ -198,6 +198,7 @@ class ExactCorrectionFn(Function):
 FORCE_SIMT = 1
 TENSOR_CORE = 2
 REUSE_LOCAL = 8
+EXACT = 32
 
 _workspaces = {}
 
@@ -221,7 +222,8 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
                rope_freqs: Tensor, gating_c: float, omega_thresh: float, adt_delta: float,
                adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int,
                chunk_size: int, h0: Tensor = None, *, shortcut_scale: float = 0.0, pos0: int = 0,
-               return_tail_state: bool = False, flags: int = 0, out: Tensor = None, segs: int = 1):
+               return_tail_state: bool = False, flags: int = 0, out: Tensor = None, segs: int = 1,
+               semantics: str = "reference"):
     """The scan path of one CD-SSM block in a single call.
 
     Equals, in the reference (cdssm/models/block.py:181-211): DynamicsFusedFn -> NormalizeKQFn
@@ -236,7 +238,14 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
     Returns (y (B,L,H,N), final_state (B,H,N,D) float32[, tail_state]); final_state is the carry
     after the last chunk (feed it as h0 of the next chunk-aligned segment together with pos0);
     tail_state is the recurrent state after the last token (what decode_step continues from).
+    semantics="exact" runs the plain sequential recurrence instead of the reference's chunk semantics
+    (identical inside the first chunk); h0/final_state are then the recurrent state.
     """
+    if semantics not in ("reference", "exact"):
+        raise CdssmError("semantics must be 'reference' (the reference's chunked scan, bug for bug) or "
+                         "'exact' (the sequential recurrence)")
+    if semantics == "exact":
+        flags = int(flags) | EXACT
     q = _prep(q, name="q")
     k = _prep(k, dtype=q.dtype, name="k")
     v = _prep(v, dtype=q.dtype, name="v")

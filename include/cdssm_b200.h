@@ -95,6 +95,10 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
 #define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels (the default) */
 #define CDSSM_SCAN_REUSE_LOCAL 8    /* the workspace still holds the local pass of exactly these inputs, left
                                       by cdssm_b200_scan_summary_fwd on the same workspace: skip that pass */
+#define CDSSM_SCAN_EXACT 32         /* NOT the reference's chunk semantics: the plain token-by-token recurrence
+                                      over the whole sequence (what the reference equals inside its first
+                                      chunk and what decode continues); h0/final_state/tail_state are then
+                                      the recurrent state.  One sequential walk per (batch, head, pair). */
 #define CDSSM_SCAN_TENSOR_CORE 2   /* use the single-pass tcgen05/TMA kernel: bf16, N = 2, D = C = 128,
                                       no tail_state; CDSSM_ERR_UNSUPPORTED for other sizes */
 

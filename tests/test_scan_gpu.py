@@ -193,3 +193,41 @@ def test_segmented_scan_equals_unsegmented(ops, orc, dtype, mask, tol, B, H, L, 
     got = to_np(decay)
     assert np.abs(got[..., 0::2] - gam.real).max() <= 2e-2 * max(np.abs(gam).max(), 1e-6)
     assert np.abs(got[..., 1::2] - gam.imag).max() <= 2e-2 * max(np.abs(gam).max(), 1e-6)
+
+
+# ---------------------------------------------------------------- exact (sequential) semantics
+@pytest.mark.parametrize("dtype,mask,tol", [(torch.float32, 0, FP32_TOL), (torch.bfloat16, 9, BF16_TOL / 2)])
+@pytest.mark.parametrize("B,H,L,D,N", [(2, 3, 300, 64, 2), (1, 2, 200, 128, 2), (1, 2, 70, 40, 4)])
+def test_exact_semantics_is_the_sequential_recurrence(ops, orc, dtype, mask, tol, B, H, L, D, N):
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=L, bf16=mask != 0, context_length=512)
+    s0 = np.random.default_rng(L).standard_normal((B, H, N, D)).astype(np.float32) * 0.5
+    wy, wst = orc.scan_recurrent(inp["q"], inp["k"], inp["v"], inp["gate_raw"], inp["log_dt_scale"],
+                                 inp["rope_freqs"], inp["consts"], N, state=s0, shortcut_scale=0.2, pos0=3,
+                                 round_bf16=mask)
+    y, fin, tail = run_fused(ops, inp, dtype, N, 64, h0=s0, shortcut_scale=0.2, pos0=3, semantics="exact",
+                             return_tail_state=True)
+    assert rel_err(to_np(y), wy) <= tol
+    assert rel_err(to_np(fin), wst) <= max(tol / 4, 1e-5) and torch.equal(fin, tail)
+    # the reference's chunk semantics equal the recurrence inside the first chunk when the carry-in is
+    # zero (a non-zero carry is read one step early, exact_correction.cu:90-94) and differ beyond it
+    wy0, _ = orc.scan_recurrent(inp["q"], inp["k"], inp["v"], inp["gate_raw"], inp["log_dt_scale"],
+                                inp["rope_freqs"], inp["consts"], N, shortcut_scale=0.2, pos0=3, round_bf16=mask)
+    yr, _ = run_fused(ops, inp, dtype, N, 64, shortcut_scale=0.2, pos0=3)
+    if L > 64:
+        assert rel_err(to_np(yr), wy0) > 10 * tol
+    assert rel_err(to_np(yr[:, :64]), wy0[:, :64]) <= tol
+
+
+def test_exact_prefill_feeds_decode_beyond_one_chunk(ops, orc):
+    B, H, D, N, T0, T1 = 2, 2, 64, 2, 150, 10
+    inp = orc.make_inputs(B, H, T0 + T1, D, N=N, seed=12, context_length=256)
+    wy, _ = orc.scan_recurrent(inp["q"], inp["k"], inp["v"], inp["gate_raw"], inp["log_dt_scale"],
+                               inp["rope_freqs"], inp["consts"], N)
+    head = {k: (v[:, :T0] if getattr(v, "ndim", 0) >= 3 else v) for k, v in inp.items()}
+    y0, state = run_fused(ops, head, torch.float32, N, 64, semantics="exact")
+    f = lambda x: to_dev(x, torch.float32)
+    q, k, v, g = f(inp["q"]), f(inp["k"]), f(inp["v"]), f(inp["gate_raw"])
+    ys = [ops.decode_step(state, q[:, t], k[:, t], v[:, t], g[:, t], f(inp["log_dt_scale"]), f(inp["rope_freqs"]),
+                          *const_args(inp["consts"]), H, N, t) for t in range(T0, T0 + T1)]
+    y = torch.cat([y0, torch.stack(ys, 1)], 1)
+    assert rel_err(to_np(y), wy) <= FP32_TOL
