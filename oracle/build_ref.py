@@ -8,7 +8,7 @@ cannot load on a B200, so the same sources are compiled here for sm_100 with the
 reference's other flags (`-O3 --use_fast_math`).  The result is a torch extension
 module `cdssm_ref_C` exposing the twelve `*_cuda` functions of cdssm/csrc/binding.cpp:130-202.
 
-Usage:  python oracle/build_ref.py [reference_root]
+Usage:  python oracle/build_ref.py [reference_root]   (default: $CDSSM_REFERENCE_ROOT or the mounted checkout)
 The sources are never copied into this repository; only the built `.so` lands in
 oracle/_ref/ (git-ignored).
 """
@@ -26,7 +26,8 @@ def ref_so_path():
     return os.path.join(OUT, "cdssm_ref_C.so")
 
 
-def build(reference_root="/root/reference", verbose=False):
+def build(reference_root=None, verbose=False):
+    reference_root = reference_root or os.environ.get("CDSSM_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
     csrc = os.path.join(reference_root, "cdssm", "csrc")
     if not os.path.isdir(csrc):
         raise FileNotFoundError(f"reference sources not found under {reference_root}")

@@ -4,7 +4,7 @@ sources are mounted):
 
     python tests/golden/make_golden_ref.py [outdir]
 
-Writes ref_<case>.npz files (default: gpurun_out/golden/); copy them into tests/golden/.
+Writes ref_<case>.npz files (default: ./golden_out/); copy them into tests/golden/.
 """
 import os
 import sys
@@ -24,7 +24,7 @@ def main():
     ref = load_ref()
     if ref is None:
         raise SystemExit("oracle/_ref/cdssm_ref_C.so not built")
-    out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(out, exist_ok=True)
     for name, case in CASES.items():
         res = run_reference(ref, case, oracle)
