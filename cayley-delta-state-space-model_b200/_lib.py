@@ -36,6 +36,7 @@ SIGNATURES = {
     "cdssm_b200_scan_fused_fwd": (_I, [_P] * 11 + [_c_size_t] + [_F] * 6 + [_I] * 9 + [_P]),
     "cdssm_b200_scan_summary_fwd": (_I, [_P] * 9 + [_c_size_t] + [_F] * 5 + [_I] * 9 + [_P]),
     "cdssm_b200_scan_fused_segmented_fwd": (_I, [_P] * 10 + [_c_size_t] + [_F] * 6 + [_I] * 10 + [_P]),
+    "cdssm_b200_compose_carries": (_I, [_P] * 6 + [_I] * 5 + [_c_int64, _c_int64, _P]),
     "cdssm_b200_scan_fused_fwd_noalloc": (_I, [_P] * 10 + [_F] * 6 + [_I] * 9 + [_P]),
     "cdssm_b200_scan_fused_noalloc_max_bytes": (_c_size_t, []),
     "cdssm_b200_scan_fused_status": (_I, [_P, _P, _P]),

@@ -226,6 +226,45 @@ conv1d_silu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T
     }
 }
 
+// ---------------------------------------------------------------- carries into consecutive segments
+// One thread per (b, h, pair, d): carry_in[g] = s; s <- decay[g] (*) s + carry_out[g], g = 0..S-1.
+// Segment g of batch element b is found at index b*batch_stride + g*seg_stride (in segments), so the
+// same kernel serves segments stored as consecutive batch rows and summaries gathered rank by rank.
+__global__ void __launch_bounds__(128)
+compose_carries_kernel(const float* __restrict__ decay, const float* __restrict__ carry_out,
+                       const float* __restrict__ h0, float* __restrict__ carry_in,
+                       float* __restrict__ final_state, float* __restrict__ total_decay, int B, int S, int H,
+                       int D, int N, long long batch_stride, long long seg_stride) {
+    const int NH = N >> 1;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)B * H * NH * D) return;
+    const int d = (int)(idx % D);
+    const int j = (int)((idx / D) % NH);
+    const int hd = (int)((idx / ((long long)D * NH)) % H);
+    const int b = (int)(idx / ((long long)D * NH * H));
+    const long long so = (((long long)b * H + hd) * N + 2 * j) * D + d;
+    float sr = 0.f, si = 0.f, pr = 1.f, pi = 0.f;
+    if (h0) { sr = h0[so]; si = h0[so + D]; }
+    for (int g = 0; g < S; g++) {
+        const long long seg = (long long)b * batch_stride + (long long)g * seg_stride;
+        const long long o = ((seg * H + hd) * N + 2 * j) * D + d;
+        if (carry_in) { carry_in[o] = sr; carry_in[o + D] = si; }
+        const float re = decay[(seg * H + hd) * N + 2 * j], im = decay[(seg * H + hd) * N + 2 * j + 1];
+        const float nr = re * sr - im * si + carry_out[o];
+        const float ni = re * si + im * sr + carry_out[o + D];
+        sr = nr;
+        si = ni;
+        const float qr = re * pr - im * pi, qi = re * pi + im * pr;
+        pr = qr;
+        pi = qi;
+    }
+    if (final_state) { final_state[so] = sr; final_state[so + D] = si; }
+    if (total_decay && d == 0) {
+        total_decay[((long long)b * H + hd) * N + 2 * j] = pr;
+        total_decay[((long long)b * H + hd) * N + 2 * j + 1] = pi;
+    }
+}
+
 }  // namespace cdssm
 
 using namespace cdssm;
@@ -327,5 +366,18 @@ extern "C" int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, con
     if (grid.y > 65535) return CDSSM_ERR_UNSUPPORTED;
     DISPATCH_DTYPE(dtype, (conv1d_silu_fwd_kernel<T, kSeg><<<grid, 128, 0, (cudaStream_t)stream>>>(
                               (const T*)x, (const T*)weight, (const T*)bias, (T*)out, L, Dm)));
+    return check_launch();
+}
+
+extern "C" int cdssm_b200_compose_carries(const float* decay, const float* carry_out, const float* h0,
+                                          float* carry_in, float* final_state, float* total_decay, int B,
+                                          int S, int H, int D, int N, int64_t batch_stride,
+                                          int64_t seg_stride, void* stream) {
+    if (!decay || !carry_out || B < 0 || S < 0) return CDSSM_ERR_BAD_ARG;
+    if (int rc = check_scan_dims(1, H, D, N)) return rc;
+    const long long threads = (long long)B * H * (N / 2) * D;
+    if (threads == 0) return CDSSM_OK;
+    compose_carries_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+        decay, carry_out, h0, carry_in, final_state, total_decay, B, S, H, D, N, batch_stride, seg_stride);
     return check_launch();
 }

@@ -21,7 +21,7 @@ from ._lib import CdssmError, check
 
 __all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
            "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
-           "scan_fused_workspace_bytes", "scan_fused_status", "scan_summary", "scan_fused_long",
+           "scan_fused_workspace_bytes", "scan_fused_status", "scan_summary", "scan_fused_long", "compose_carries",
            "CdssmError"]
 
 _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
@@ -408,21 +408,15 @@ def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_sc
     carry, decay = scan_summary(seg(k), seg(v), seg(gate_raw), log_dt_scale, rope_freqs, *consts, n_heads, N, C,
                                 pos0=base, segs=S)
     if ev: ev[1].record()
-    carry = carry.view(B, S, H, N, D).transpose(0, 1)          # (S,B,H,N,D)
-    decay = decay.view(B, S, H, N).transpose(0, 1)
     if world > 1:
-        # this rank's piece as one summary, exchanged with the other ranks
-        _, piece_out = sharding.compose_carries(decay, carry)
-        piece_dec = decay[0]
-        for g in range(1, S):
-            piece_dec = sharding.complex_mul_pairs(decay[g], piece_dec)
-        decs, outs = sharding.exchange_summaries(piece_dec.contiguous(), piece_out.contiguous(), group)
-        ins, _ = sharding.compose_carries(decs, outs, h0)
-        h_in = ins[rank]
+        # this rank's piece as one summary, exchanged with the other ranks (one small all-gather)
+        _, piece_out, piece_dec = compose_carries(decay, carry, None, B, S, layout="rows", want_carry_in=False)
+        decs, outs = sharding.exchange_summaries(piece_dec, piece_out, group)
+        ins, _, _ = compose_carries(decs, outs, h0, B, world, layout="gathered")
+        h_in = ins[rank].contiguous()
     else:
         h_in = h0
-    carry_in, final = sharding.compose_carries(decay, carry, h_in)
-    h_rows = carry_in.transpose(0, 1).contiguous().view(B * S, H, N, D)
+    h_rows, final, _ = compose_carries(decay, carry, h_in, B, S, layout="rows")
     if ev: ev[2].record()
     y, _ = scan_fused(seg(q), seg(k), seg(v), seg(gate_raw), log_dt_scale, rope_freqs, *consts, n_heads, N, C,
                       h_rows, shortcut_scale=shortcut_scale, pos0=base, segs=S,
@@ -433,3 +427,27 @@ def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_sc
         timings.update(summary_ms=ev[0].elapsed_time(ev[1]), handoff_ms=ev[1].elapsed_time(ev[2]),
                        scan_ms=ev[2].elapsed_time(ev[3]))
     return y.view(B, L, H, N), final
+
+
+def compose_carries(decay: Tensor, carry_out: Tensor, h0, batch: int, segments: int, layout: str = "rows",
+                    want_carry_in: bool = True):
+    """Chain segment summaries on the GPU: carry_in[g] = s; s <- decay[g] * s + carry_out[g].
+
+    layout "rows": decay (B*S,H,N), carry_out (B*S,H,N,D) are the rows of a segmented batch;
+    layout "gathered": decay (S,B,H,N), carry_out (S,B,H,N,D) (one summary per rank).
+    Returns (carry_in like carry_out or None, final (B,H,N,D), total_decay (B,H,N))."""
+    decay = _prep(decay, dtype=torch.float32, name="decay")
+    carry_out = _prep(carry_out, dtype=torch.float32, name="carry_out")
+    H, N, D = carry_out.shape[-3:]
+    B, S = int(batch), int(segments)
+    bs, ss = (S, 1) if layout == "rows" else (1, B)
+    if h0 is not None:
+        h0 = _prep(h0, dtype=torch.float32, name="h0")
+    dev = carry_out.device
+    cin = torch.empty_like(carry_out) if want_carry_in else None
+    final = torch.empty(B, H, N, D, dtype=torch.float32, device=dev)
+    tot = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.lib().cdssm_b200_compose_carries(_p(decay), _p(carry_out), _p(h0), _p(cin), _p(final), _p(tot),
+                                                    B, S, H, D, N, bs, ss, _stream()), "compose_carries")
+    return cin, final, tot

@@ -162,6 +162,17 @@ CDSSM_API int cdssm_b200_scan_fused_segmented_fwd(const void* q, const void* k, 
                                                   int D, int N, int C, int pos0, int segs, int dtype,
                                                   int flags, void* stream);
 
+/* Chains segment summaries: carry_in[g] = s, then s <- decay[g] (*) s + carry_out[g] for g = 0..S-1,
+ * starting from s = h0 (NULL = zero).  decay (.,H,N), carry_out / carry_in (.,H,N,D) float32 are indexed
+ * by segment; segment g of batch element b sits at index b*batch_stride + g*seg_stride, e.g.
+ * (S, 1) for the rows of a segmented batch and (1, B) for summaries gathered rank by rank.
+ * carry_in, final_state (B,H,N,D) and total_decay (B,H,N) (the product of all decays) may be NULL.
+ * No reference counterpart. */
+CDSSM_API int cdssm_b200_compose_carries(const float* decay, const float* carry_out, const float* h0,
+                                         float* carry_in, float* final_state, float* total_decay, int B,
+                                         int S, int H, int D, int N, int64_t batch_stride,
+                                         int64_t seg_stride, void* stream);
+
 /* The fused scan for callers that cannot allocate device memory (a server whose pool already owns
  * the whole GPU, a plugin barred from the CUDA allocator, code that must not trigger the
  * device-wide synchronisation of cudaMalloc).  Same arguments and results as
