@@ -13,7 +13,8 @@ extern "C" int cdssm_b200_last_cuda_error(void) { return cdssm::last_cuda_error_
 
 // Performance-debugging hook (not part of the public header): device buffer of 8*5*16 int64 that
 // receives clock64 stamps of the tensor-core scan's first CTA, or NULL to switch tracing off.
-namespace cdssm { void scan_tc_set_trace(long long* p); }
+namespace cdssm { void scan_tc_set_trace(long long* p); void scan_tc4_set_trace(long long* p); }
 extern "C" __attribute__((visibility("default"))) void cdssm_b200_debug_set_trace(void* p) {
     cdssm::scan_tc_set_trace(static_cast<long long*>(p));
+    cdssm::scan_tc4_set_trace(static_cast<long long*>(p));
 }

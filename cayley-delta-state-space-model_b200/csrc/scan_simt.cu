@@ -111,6 +111,7 @@ struct ScanArgs {
     float* total_decay;   // (B,H,N) or NULL: product over the chunks of the (rounded) chunk decays
     int segs;             // batch rows are `segs` consecutive segments of longer sequences
     int run_local;        // 0: the workspace already holds this input's local pass
+    int run_output;       // 0: stop after the carry pass (another kernel writes y)
     int publish;          // 0: summary only, the carry pass leaves the local results in place
     float* ws_gamma;   // (B,NC,H,NP,2)
     float* ws_state;   // (B,NC,H,NP,2,D): z_{C-1} after the local pass, s_c after the carry pass
@@ -570,7 +571,7 @@ static int launch_simt(const ScanArgs& a, cudaStream_t st) {
     const long long th = (long long)a.B * a.H * (a.N / 2) * a.D;
     scan_carry_kernel<T><<<(unsigned)((th + 127) / 128), 128, 0, st>>>(a);
     if (int rc = check_launch()) return rc;
-    if (a.y == nullptr) return CDSSM_OK;   // summary only: carry out and decay product
+    if (a.y == nullptr || !a.run_output) return CDSSM_OK;   // summary only, or y comes from another kernel
     scan_walk_kernel<T, kCols, kLanes, true><<<blocks, kSimtThreads, smem, st>>>(a);
     return check_launch();
 }
@@ -731,6 +732,12 @@ int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_
                   const float* rope_freqs, const float* h0, void* y, float* final_state, int* status,
                   const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
                   cudaStream_t st);
+// scan_tc4.cu
+bool scan_tc4_supported(int D, int N, int C, int H, int dtype);
+int scan_tc4_pass(bool output, const void* q, const void* k, const void* v, const void* gate_raw,
+                  const float* log_dt_scale, const float* rope_freqs, float* ws_gamma, float* ws_state, void* y,
+                  int* status, const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
+                  cudaStream_t st);
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -788,6 +795,7 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     a.y = y; a.final_state = final_state; a.tail_state = tail_state;
     a.total_decay = total_decay; a.segs = segs;
     a.run_local = (flags & CDSSM_SCAN_REUSE_LOCAL) ? 0 : 1;
+    a.run_output = 1;
     a.publish = summary_only ? 0 : 1;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
     a.shortcut_scale = shortcut_scale;
@@ -810,6 +818,25 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
             rc = check_cuda(cudaMemcpyAsync(extra, a.final_state, sizeof(float) * (size_t)B * H * N * D,
                                             cudaMemcpyDeviceToDevice, st));
         return rc;
+    }
+    if ((flags & CDSSM_SCAN_TENSOR_CORE4) && !(flags & CDSSM_SCAN_FORCE_SIMT) && !summary_only) {
+        // Four-chain tensor-core kernels for the local and the output pass; the carry pass between them is
+        // the CUDA-core kernel.  (Bits 256 / 512 keep the CUDA-core local / output pass: used by the tests
+        // to check each tensor-core pass on its own.)
+        if (tail_state != nullptr || !scan_tc4_supported(D, N, C, H, dtype)) return CDSSM_ERR_UNSUPPORTED;
+        cudaStream_t st = (cudaStream_t)stream;
+        const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
+        if (a.run_local && tc_local) {
+            if (int rc = scan_tc4_pass(false, q, k, v, gate_raw, log_dt_scale, rope_freqs, a.ws_gamma, a.ws_state,
+                                       nullptr, status, a.dc, shortcut_scale, B, L, H, pos0, segs, st))
+                return rc;
+            a.run_local = 0;
+        }
+        a.run_output = tc_output ? 0 : 1;
+        if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;
+        if (!tc_output) return CDSSM_OK;
+        return scan_tc4_pass(true, q, k, v, gate_raw, log_dt_scale, rope_freqs, a.ws_gamma, a.ws_state, y, status,
+                             a.dc, shortcut_scale, B, L, H, pos0, segs, st);
     }
     return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
 }

@@ -199,6 +199,7 @@ FORCE_SIMT = 1
 TENSOR_CORE = 2
 REUSE_LOCAL = 8
 EXACT = 32
+TENSOR_CORE4 = 64
 
 _workspaces = {}
 

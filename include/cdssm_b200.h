@@ -101,6 +101,9 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
                                       the recurrent state.  One sequential walk per (batch, head, pair). */
 #define CDSSM_SCAN_TENSOR_CORE 2   /* use the single-pass tcgen05/TMA kernel: bf16, N = 2, D = C = 128,
                                       no tail_state; CDSSM_ERR_UNSUPPORTED for other sizes */
+#define CDSSM_SCAN_TENSOR_CORE4 64 /* local and output pass as tcgen05/TMA kernels that walk four heads' chunks
+                                      per thread block in 32-token sub-blocks: bf16, N = 2, D = C = 128,
+                                      H a multiple of 4, no tail_state; CDSSM_ERR_UNSUPPORTED otherwise */
 
 /* Bytes of workspace cdssm_b200_scan_fused_fwd needs for these sizes (0 on bad sizes). */
 CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C);

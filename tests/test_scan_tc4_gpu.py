@@ -1,0 +1,89 @@
+"""The four-chain tcgen05/TMA scan kernels (bf16, N = 2, D = C = 128, H % 4 == 0) against the CPU oracle
+and against the CUDA-core kernels, through the C ABI.  Flag bits 256 / 512 keep the CUDA-core local /
+output pass, so each tensor-core pass is also checked on its own."""
+import numpy as np
+import pytest
+import torch
+
+from test_scan_gpu import oracle_scan, run_fused, unnormalise
+from util import BF16_TOL, rel_err, to_np
+
+pytestmark = pytest.mark.gpu
+N, C, D = 2, 128, 128
+KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT = 256, 512
+
+
+def _inputs(orc, B, H, L, seed, scale=True):
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=seed, bf16=True, context_length=max(L, 2))
+    if scale:
+        inp = unnormalise(inp, np.random.default_rng(seed))
+        inp["q"], inp["k"] = orc.bf16_round(inp["q"]), orc.bf16_round(inp["k"])
+    return inp
+
+
+@pytest.mark.parametrize("extra", [KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT, 0])
+@pytest.mark.parametrize("B,H,L", [(1, 4, 128), (1, 4, 256), (2, 8, 300), (1, 4, 1), (1, 4, 129), (2, 12, 1024),
+                                   (3, 32, 512)])
+def test_tc4_matches_oracle_and_simt(ops, orc, B, H, L, extra):
+    inp = _inputs(orc, B, H, L, seed=L + H)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.TENSOR_CORE4 | extra)
+    assert ops.scan_fused_status() == 0
+    ys, fs = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.FORCE_SIMT)
+    wy, _ = oracle_scan(orc, inp, N, C, orc.ROUND_REFERENCE)
+    wy13, wf13 = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE)
+    assert rel_err(to_np(y), wy) <= BF16_TOL
+    assert rel_err(to_np(y), wy13) <= BF16_TOL / 2
+    assert rel_err(to_np(y), to_np(ys)) <= BF16_TOL / 2
+    scale = max(np.abs(wf13).max(), 1e-3)
+    assert np.abs(to_np(fin) - wf13).max() <= 2e-2 * scale
+    assert np.abs(to_np(fin) - to_np(fs)).max() <= 2e-2 * scale
+
+
+def test_tc4_h0_shortcut_composition(ops, orc):
+    B, H, L = 2, 4, 512
+    inp = _inputs(orc, B, H, L, seed=77, scale=False)
+    h0 = np.random.default_rng(1).standard_normal((B, H, N, D)).astype(np.float32)
+    wy, wfin = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE, h0=h0, shortcut_scale=0.6)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6, flags=ops.TENSOR_CORE4)
+    assert ops.scan_fused_status() == 0
+    assert rel_err(to_np(y), wy) <= BF16_TOL / 2
+    assert rel_err(to_np(fin), wfin) <= 2e-2
+    cut = lambda s: {k: (v[:, s] if getattr(v, "ndim", 0) >= 3 else v) for k, v in inp.items()}
+    y1, f1 = run_fused(ops, cut(slice(0, 256)), torch.bfloat16, N, C, h0=h0, shortcut_scale=0.6, flags=ops.TENSOR_CORE4)
+    y2, f2 = run_fused(ops, cut(slice(256, None)), torch.bfloat16, N, C, h0=to_np(f1), shortcut_scale=0.6, pos0=256,
+                       flags=ops.TENSOR_CORE4)
+    assert torch.equal(torch.cat([y1, y2], 1), y) and torch.equal(f2, fin)
+
+
+def test_tc4_many_items_per_block(ops, orc):
+    """More (chunk, head group) items than resident thread blocks: the persistent loop and its barrier
+    phases across items."""
+    B, H, L = 2, 8, 128 * 96
+    inp = _inputs(orc, B, H, L, seed=9)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.TENSOR_CORE4)
+    assert ops.scan_fused_status() == 0
+    ys, fs = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.FORCE_SIMT)
+    assert rel_err(to_np(y), to_np(ys)) <= BF16_TOL / 2
+    assert rel_err(to_np(fin), to_np(fs)) <= 2e-2
+
+
+def test_tc4_deterministic_and_in_bounds(ops, orc):
+    B, H, L = 1, 4, 384
+    inp = _inputs(orc, B, H, L, seed=5)
+    n = B * L * H * N
+    big = torch.full((n + 512,), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = big[256:256 + n].view(B, L, H, N)
+    y1, f1 = run_fused(ops, inp, torch.bfloat16, N, C, out=out, flags=ops.TENSOR_CORE4)
+    y1 = y1.clone()
+    y2, f2 = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.TENSOR_CORE4)
+    assert torch.equal(y1, y2) and torch.equal(f1, f2)
+    assert bool((big[:256] == 7).all()) and bool((big[256 + n:] == 7).all())
+
+
+def test_tc4_flag_rejects_unsupported_sizes(ops, orc):
+    inp = orc.make_inputs(1, 2, 64, 64, N=2, seed=1, bf16=True)
+    with pytest.raises(RuntimeError):
+        run_fused(ops, inp, torch.bfloat16, 2, 64, flags=ops.TENSOR_CORE4)
+    inp = orc.make_inputs(1, 3, 128, 128, N=2, seed=1, bf16=True)   # H not a multiple of 4
+    with pytest.raises(RuntimeError):
+        run_fused(ops, inp, torch.bfloat16, 2, 128, flags=ops.TENSOR_CORE4)
