@@ -734,10 +734,11 @@ int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_
                   cudaStream_t st);
 // scan_tc4.cu
 bool scan_tc4_supported(int D, int N, int C, int H, int dtype);
-int scan_tc4_pass(bool output, const void* q, const void* k, const void* v, const void* gate_raw,
-                  const float* log_dt_scale, const float* rope_freqs, float* ws_gamma, float* ws_state, void* y,
-                  int* status, const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
-                  cudaStream_t st);
+size_t scan_tc4_record_bytes(int B, int L, int H);
+int scan_tc4_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
+                      void* rec, const DynConsts& dc, int B, int L, int H, int pos0, int segs, cudaStream_t st);
+int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, float* ws_gamma, float* ws_state,
+                  void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st);
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -746,7 +747,10 @@ extern "C" size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int
     if (B <= 0 || L <= 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1) || C <= 0) return 0;
     const size_t NC = ((size_t)L + C - 1) / C;
     const size_t units = (size_t)B * NC * H * (N / 2);
-    return 256 + align256(units * 2 * sizeof(float)) + align256(units * 2 * D * sizeof(float));
+    size_t bytes = 256 + align256(units * 2 * sizeof(float)) + align256(units * 2 * D * sizeof(float));
+    // per-token records of the four-chain tensor-core kernels (the data type is not known here)
+    if (scan_tc4_supported(D, N, C, H, CDSSM_BF16)) bytes += align256(scan_tc4_record_bytes(B, L, H));
+    return bytes;
 }
 
 extern "C" int cdssm_b200_scan_fused_status(const void* workspace, int* status_host, void* stream) {
@@ -826,17 +830,19 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
         if (tail_state != nullptr || !scan_tc4_supported(D, N, C, H, dtype)) return CDSSM_ERR_UNSUPPORTED;
         cudaStream_t st = (cudaStream_t)stream;
         const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
+        void* rec = reinterpret_cast<char*>(a.ws_state) + align256((size_t)a.units * 2 * D * sizeof(float));
+        if (int rc = scan_tc4_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, pos0, segs, st))
+            return rc;
         if (a.run_local && tc_local) {
-            if (int rc = scan_tc4_pass(false, q, k, v, gate_raw, log_dt_scale, rope_freqs, a.ws_gamma, a.ws_state,
-                                       nullptr, status, a.dc, shortcut_scale, B, L, H, pos0, segs, st))
+            if (int rc = scan_tc4_pass(false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale, B, L,
+                                       H, st))
                 return rc;
             a.run_local = 0;
         }
         a.run_output = tc_output ? 0 : 1;
         if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;
         if (!tc_output) return CDSSM_OK;
-        return scan_tc4_pass(true, q, k, v, gate_raw, log_dt_scale, rope_freqs, a.ws_gamma, a.ws_state, y, status,
-                             a.dc, shortcut_scale, B, L, H, pos0, segs, st);
+        return scan_tc4_pass(true, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L, H, st);
     }
     return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
 }

@@ -36,7 +36,8 @@ namespace tc4 {
 constexpr int kC = 128, kD = 128, kSub = 32, kSteps = kC / kSub;
 constexpr int kThreads = 160;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColG = 0, kColP = 32, kColKappa = 64, kColRho = 96, kColUp = 128;
+// G and P: 64 columns each - a pair of heads per UMMA, a thread reads the 32 columns of its own head
+constexpr uint32_t kColG = 0, kColP = 64, kColQQ = 128, kColKappa = 160, kColRho = 192, kColUp = 224;
 constexpr uint32_t kSlab = 128 * 128;          // 64 bf16 columns x 128 rows
 constexpr uint32_t kTile = 2 * kSlab;          // 32 KB
 constexpr uint32_t kSmallSlab = 32 * 128;      // 32-row operand tiles: 4 KB per 64 columns
@@ -55,16 +56,14 @@ struct __align__(1024) Smem {
 };
 
 struct Args {
-    const __nv_bfloat16 *v, *gate_raw;
-    const float *log_dt_scale, *rope_freqs;
+    const uint4* rec;            // per (token, head) record from the dynamics pre-pass (see tc4_dynamics_kernel)
     float* ws_gamma;             // (B,NC,H,2): written by the local pass
     float* ws_state;             // (B,NC,H,2,D): local pass writes z_{C-1}; the output pass reads the carry s_c
     __nv_bfloat16* y;
     int* status;
     long long* trace;
-    DynConsts dc;
     float shortcut_scale;
-    int B, L, H, NC, pos0, segs;
+    int B, L, H, NC;
     int HG, items;               // head groups of four; items = B * NC * HG (one chunk of four heads each)
 };
 
@@ -104,6 +103,80 @@ __device__ __forceinline__ void umma_bf16_unit(uint32_t d_tmem, uint64_t a_desc,
 }
 
 
+// The producer warp runs its event loop with all 32 lanes (warp-uniform values keep the descriptors in
+// uniform registers); only one elected lane issues each asynchronous instruction.
+__device__ __forceinline__ void umma_bf16_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_unit_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 bool accumulate, uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(m0), "r"(m1), "r"(m2),
+          "r"(m3)
+        : "memory");
+}
+// Every shared-memory descriptor used here has the same upper word (stride between eight-row groups
+// 1024 bytes, Blackwell descriptor version, 128-byte swizzle), so only the lower word (start address and
+// leading-dimension offset, both in 16-byte units) is carried around and advanced.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ void umma_lo_e(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 ad, bd;\n\t"
+        "mov.b64 ad, {%1, %5};\n\t"
+        "mov.b64 bd, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(acc), "r"(kDescHi)
+        : "memory");
+}
+__device__ __forceinline__ void umma_lo_unit_e(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t acc, uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 ad, bd;\n\t"
+        "mov.b64 ad, {%1, %9};\n\t"
+        "mov.b64 bd, {%2, %9};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(acc), "r"(m0), "r"(m1), "r"(m2), "r"(m3), "r"(kDescHi)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_e(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t e;
+    asm volatile(
+        "{\n\t.reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, e;\n\t}"
+        : "=r"(e));
+    return e != 0;
+}
+__device__ __forceinline__ bool warp_test(uint64_t* bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_test(bar, parity));
+}
+
 // ------------------------------------------------------------------------------------------
 // Producer (one elected lane of warp 4): TMA and UMMA issue, event driven.  The CTA's work is a flat
 // sequence of sub-block steps g = 0 .. 4 * n_items - 1; item (g >> 2) is chunk c of heads h0 .. h0 + 3
@@ -114,6 +187,7 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
     volatile int* ab = &sm.abort_flag;
     const uint32_t tm = sm.tmem_base;
     constexpr uint32_t idesc32 = umma_idesc_bf16(128, 32, false, false);
+    constexpr uint32_t idesc64 = umma_idesc_bf16(128, 64, false, false);
     constexpr uint32_t idesc_up = umma_idesc_bf16(128, 32, true, false);
     const uint32_t kaddr[2] = {smem_u32(sm.k[0]), smem_u32(sm.k[1])};
     const uint32_t qaddr = smem_u32(sm.q), saddr = smem_u32(sm.s_tile), oaddr = smem_u32(sm.o_tile);
@@ -125,101 +199,133 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
         const int item = (int)blockIdx.x + (g >> 2) * (int)gridDim.x;
         const int h0 = (item % a.HG) * 4, c = (item / a.HG) % a.NC, b = item / (a.HG * a.NC);
         const int l0 = c * kC + (g & 3) * kSub;
-        mbar_arrive_expect_tx(bar, kTile);
+        if (elect_one()) {
+            mbar_arrive_expect_tx(bar, kTile);
 #pragma unroll 1
-        for (int j = 0; j < 4; j++) {
-            tma_load_4d(dst + j * kSub * 128, tmap, bar, 0, h0 + j, l0, b);
-            tma_load_4d(dst + kSlab + j * kSub * 128, tmap, bar, 64, h0 + j, l0, b);
+            for (int j = 0; j < 4; j++) {
+                tma_load_4d(dst + j * kSub * 128, tmap, bar, 0, h0 + j, l0, b);
+                tma_load_4d(dst + kSlab + j * kSub * 128, tmap, bar, 64, h0 + j, l0, b);
+            }
         }
-    };
-    auto kmaj = [](uint32_t base, uint32_t slab_bytes, int j, uint32_t row_off) {
-        return umma_desc_sw128(base + (uint32_t)(j >> 2) * slab_bytes + (uint32_t)(j & 3) * 32 + row_off, 16, 1024);
+        __syncwarp();
     };
     if (NS > 0) {
         load_tile(sm.k[0], tmK, &sm.full_k[0], 0); pend_k[0] = true;
         if (kOutput) { load_tile(sm.q, tmQ, &sm.full_q, 0); pend_q = true; }
         load_tile(sm.k[1], tmK, &sm.full_k[1], 1); pend_k[1] = true;
     }
-    int i_gp = 0, i_kr = 0, i_up = 0, i_lq = 1, i_lk = 2;
+    // Lower descriptor words of the operands at k-step 0.  A k-step is 32 bytes (+2); after four of them the
+    // next 64-column slab starts (K-major tiles).  The MN-major K tile advances 16 tile rows = 2 KB per step.
+    const uint32_t lK[2] = {desc_lo(kaddr[0], 16), desc_lo(kaddr[1], 16)};
+    const uint32_t lKt[2] = {desc_lo(kaddr[0], kSlab), desc_lo(kaddr[1], kSlab)};
+    const uint32_t lQ = desc_lo(qaddr, 16), lS = desc_lo(saddr, 16), lO = desc_lo(oaddr, 16);
+    constexpr uint32_t kBigJump = (kSlab >> 4) - 8, kSmallJump = (kSmallSlab >> 4) - 8;
+    int i_gp = 0, gp_u = 0, i_kr = 0, i_up = 0, i_lq = 1, i_lk = 2;
     bool k_ok = false, q_ok = !kOutput;
     uint64_t last = global_ns();
     uint32_t idle = 0;
+#define TC4_PSTAMP(n, idx) do { if (a.trace && (threadIdx.x & 31) == 0 && blockIdx.x == 0 && (n) < 16) a.trace[((n) * 5 + 4) * 16 + (idx)] = clock64(); } while (0)
     auto par = [](int n) { return (uint32_t)(n & 1); };
+    // Tasks in order of urgency: the state update and kappa / rho sit on the compute warps' critical path,
+    // the tile loads and the Gram blocks of the NEXT step do not; the Gram blocks are issued one head at a
+    // time so that an urgent task never waits behind more than sixteen UMMAs.
     while (i_up < NS) {
         bool progress = false;
-        if (i_gp < NS) {   // diagonal Gram blocks of step i_gp
-            const int n = i_gp, st = n & 1;
-            if (!k_ok && mbar_test(&sm.full_k[st], (n >> 1) & 1)) { k_ok = true; pend_k[st] = false; }
-            if (!q_ok && mbar_test(&sm.full_q, par(n))) { q_ok = true; pend_q = false; }
-            if (k_ok && q_ok && (n == 0 || mbar_test(&sm.gp_free, par(n - 1)))) {
-                tc_fence_after();
-#pragma unroll 1
-                for (int u = 0; u < 4; u++) {
-#pragma unroll 1
-                    for (int j = 0; j < 8; j++)
-                        umma_bf16_unit(tm + kColG, kmaj(kaddr[st], kSlab, j, 0),
-                                       kmaj(kaddr[st], kSlab, j, u * kSub * 128), idesc32, j > 0, u);
-                    if (kOutput) {
-#pragma unroll 1
-                        for (int j = 0; j < 8; j++)
-                            umma_bf16_unit(tm + kColP, kmaj(qaddr, kSlab, j, 0),
-                                           kmaj(kaddr[st], kSlab, j, u * kSub * 128), idesc32, j > 0, u);
-                    }
-                }
-                umma_commit(&sm.mma_gp);
-                i_gp++; k_ok = false; q_ok = !kOutput; progress = true;
-            }
-        }
-        if (i_kr < i_gp && mbar_test(&sm.s_ready, par(i_kr))) {   // kappa = K S^T, rho = Q S^T
-            const int st = i_kr & 1;
-            tc_fence_after();
-#pragma unroll 1
-            for (int j = 0; j < 8; j++)
-                umma_bf16(tm + kColKappa, kmaj(kaddr[st], kSlab, j, 0), kmaj(saddr, kSmallSlab, j, 0), idesc32, j > 0);
-            if (kOutput) {
-#pragma unroll 1
-                for (int j = 0; j < 8; j++)
-                    umma_bf16(tm + kColRho, kmaj(qaddr, kSlab, j, 0), kmaj(saddr, kSmallSlab, j, 0), idesc32, j > 0);
-            }
-            umma_commit(&sm.mma_kr);
-            i_kr++; progress = true;
-        }
-        // Q tile of step n is free once its UMMAs have completed (mma_kr is committed after mma_gp of the
-        // same step, so it covers both) and every warp has read |q| from it (gp_free follows that read)
-        if (kOutput && i_lq <= i_kr && i_lq <= NS && mbar_test(&sm.mma_kr, par(i_lq - 1)) &&
-            mbar_test(&sm.gp_free, par(i_lq - 1))) {
-            if (i_lq < NS) { load_tile(sm.q, tmQ, &sm.full_q, i_lq); pend_q = true; }
-            i_lq++; progress = true;
-        }
         // state update: A = K tile read MN-major (M = d, two 64-wide groups 16 KB apart; K = tile rows,
-        // 16 per instruction = 2 KB), B = omega tile (32 rows x 128 tile rows)
-        // (issued only once the completion of the previous update has been observed below, so that the
-        // mma_up barrier is never more than one phase ahead of what this loop tests)
-        if (i_up < i_kr && i_lk - 2 >= i_up && mbar_test(&sm.omega_ready, par(i_up))) {
+        // 16 per instruction = 2 KB), B = omega tile (32 rows x 128 tile rows).  Issued only once the
+        // completion of the previous update has been observed (i_lk), so that the mma_up barrier is never
+        // more than one phase ahead of what this loop tests.
+        if (i_up < i_kr && i_lk - 2 >= i_up && warp_test(&sm.omega_ready, par(i_up))) {
             const int st = i_up & 1;
             tc_fence_after();
+            {
+                uint32_t al = lKt[st], bl = lO;
 #pragma unroll 1
-            for (int j = 0; j < 8; j++)
-                umma_bf16(tm + kColUp, umma_desc_sw128(kaddr[st] + (uint32_t)j * 2048, kSlab, 1024),
-                          kmaj(oaddr, kSmallSlab, j, 0), idesc_up, j > 0);
-            umma_commit(&sm.mma_up);
+                for (int j = 0; j < 8; j++) {
+                    umma_lo_e(tm + kColUp, al, bl, idesc_up, j);
+                    al += 2048 >> 4;
+                    bl += (j == 3) ? 2 + kSmallJump : 2;
+                }
+            }
+            umma_commit_e(&sm.mma_up);
+            TC4_PSTAMP(i_up, 3);
             i_up++; progress = true;
-        }
-        if (i_lk - 2 < i_up && i_lk - 2 < NS && mbar_test(&sm.mma_up, par(i_lk - 2))) {
-            if (i_lk < NS) { load_tile(sm.k[i_lk & 1], tmK, &sm.full_k[i_lk & 1], i_lk); pend_k[i_lk & 1] = true; }
+        } else if (i_kr < i_gp && warp_test(&sm.s_ready, par(i_kr))) {   // kappa = K S^T, rho = Q S^T
+            const int st = i_kr & 1;
+            tc_fence_after();
+            {
+                uint32_t ak = lK[st], aq = lQ, bl = lS;
+#pragma unroll 1
+                for (int j = 0; j < 8; j++) {
+                    umma_lo_e(tm + kColKappa, ak, bl, idesc32, j);
+                    if (kOutput) umma_lo_e(tm + kColRho, aq, bl, idesc32, j);
+                    const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
+                    ak += big;
+                    aq += big;
+                    bl += (j == 3) ? 2 + kSmallJump : 2;
+                }
+            }
+            umma_commit_e(&sm.mma_kr);
+            TC4_PSTAMP(i_kr, 2);
+            i_kr++; progress = true;
+        } else if (i_lk - 2 < i_up && i_lk - 2 < NS && warp_test(&sm.mma_up, par(i_lk - 2))) {
+            // the K stage of step n is free once its state update has completed
+            if (i_lk < NS) { TC4_PSTAMP(i_lk, 5); load_tile(sm.k[i_lk & 1], tmK, &sm.full_k[i_lk & 1], i_lk); pend_k[i_lk & 1] = true; }
             i_lk++; progress = true;
+        } else if (kOutput && i_lq <= i_kr && i_lq <= NS && warp_test(&sm.mma_kr, par(i_lq - 1))) {
+            // Q tile of step n is free once its UMMAs have completed (mma_kr is committed after mma_gp of the
+            // same step, so it covers both); the compute warps never read it themselves
+            if (i_lq < NS) { TC4_PSTAMP(i_lq, 4); load_tile(sm.q, tmQ, &sm.full_q, i_lq); pend_q = true; }
+            i_lq++; progress = true;
+        } else if (i_gp < NS) {   // diagonal Gram blocks of step i_gp, head gp_u
+            const int n = i_gp, st = n & 1;
+            if (!k_ok && warp_test(&sm.full_k[st], (n >> 1) & 1)) { k_ok = true; pend_k[st] = false; }
+            if (!q_ok && warp_test(&sm.full_q, par(n))) { q_ok = true; pend_q = false; }
+            if (k_ok && q_ok && (n == 0 || gp_u > 0 || warp_test(&sm.gp_free, par(n - 1)))) {
+                if (gp_u == 0) { tc_fence_after(); TC4_PSTAMP(i_gp, 0); }
+                // One pair of heads per visit: G and P of the pair as one N = 64 UMMA each (the pair's 64 lanes
+                // enabled), Q Q^T per head; k-step outermost so that independent products alternate.
+                {
+                    const uint32_t r0 = (uint32_t)gp_u * (kSub * 128 >> 4), r1 = r0 + (kSub * 128 >> 4);
+                    const uint32_t ma0 = gp_u == 0 ? 0u : 0xffffffffu, ma2 = gp_u == 2 ? 0u : 0xffffffffu;
+                    const uint32_t all = 0xffffffffu;
+                    uint32_t ak = lK[st], aq = lQ;
+                    if (gp_u == 2) TC4_PSTAMP(i_gp, 6);
+#pragma unroll 1
+                    for (int j = 0; j < 8; j++) {
+                        umma_lo_unit_e(tm + kColG, ak, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
+                        if (kOutput) {
+                            umma_lo_unit_e(tm + kColP, aq, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
+                            // Q Q^T: only its diagonal (|q_t|^2) is read
+                            umma_lo_unit_e(tm + kColQQ, aq, aq + r0, idesc32, j, ma0, all, ma2, all);
+                            umma_lo_unit_e(tm + kColQQ, aq, aq + r1, idesc32, j, all, ma0, all, ma2);
+                        }
+                        const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
+                        ak += big;
+                        aq += big;
+                    }
+                    if (gp_u == 2) TC4_PSTAMP(i_gp, 7);
+                }
+                gp_u++;
+                if (++gp_u == 4) {
+                    umma_commit_e(&sm.mma_gp);
+                    TC4_PSTAMP(i_gp, 1);
+                    gp_u = 0; i_gp++; k_ok = false; q_ok = !kOutput;
+                }
+                progress = true;
+            }
         }
         if (progress) {
             last = global_ns();
         } else if ((++idle & 7) != 0) {
-            __nanosleep(32);
-        } else if (*ab || global_ns() - last > kWaitLimitNs) {
+            __nanosleep(200);
+        } else if (__any_sync(0xffffffffu, *ab || global_ns() - last > kWaitLimitNs)) {
             code = 1 + (i_gp > i_kr) + 2 * (i_kr > i_up);
             *ab = 1;
             break;
         }
     }
-    if (code) {
+    if (code && elect_one()) {   // the lane that issued the UMMAs and the TMA loads
         atomicCAS(a.status, 0, 300 + code);
         umma_commit(&sm.drain);
         int never = 0;
@@ -228,6 +334,7 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
         if (pend_k[1]) mbar_wait(&sm.full_k[1], 0, &never), mbar_wait(&sm.full_k[1], 1, &never);
         if (pend_q) mbar_wait(&sm.full_q, 0, &never), mbar_wait(&sm.full_q, 1, &never);
     }
+    __syncwarp();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -235,271 +342,385 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
 // hand-off, column d = t of all four heads' states.
 // kOutput = false: local pass - z only; writes z_{C-1} and the chunk's decay product for the carry pass.
 // kOutput = true : output pass - z and r (r starts from the chunk's carry), writes y.
+//
+// Scaled unknowns.  With W_t = a_0 ... a_t (inside the sub-block) the decay between two tokens is the
+// ratio Gamma[t,i] = W_t / W_i, so the system (I + M) u = b, M[t,i] = beta_t Gamma[t,i] G[t,i], becomes in
+// u^_i = u_i / W_i the REAL unit-lower-triangular system
+//     u^_t = b_t / W_t - beta_t sum_{i<t} G[t,i] u^_i
+// with complex right-hand sides only, and the in-block read-out becomes two real-matrix products
+//     sum_{i<t} P[t,i] Gamma[t,i] u_i = W_t sum_{i<t} P[t,i] u^_i   (correction: W0_t, before its step).
+// One pass over the columns does both: per column four shuffles and eight FMAs.  The scaling needs
+// 1 / W_t, so a sub-block whose |W| gets small (strong decay; the zero padding behind the sequence end)
+// takes the slower walk that builds the decay products explicitly (robust_block).
 // ------------------------------------------------------------------------------------------
-#define TC4_STAMP(idx) do { if (a.trace && blockIdx.x == 0 && tl == 0 && g < 16) a.trace[(g * 4 + J) * 8 + (idx)] = clock64(); } while (0)
+// Record of one (token, head), written by the dynamics pre-pass: {a_re, a_im | vg_re, vg_im | beta, sel_C | -}
+// as bf16 pairs (all of them are bf16 values in the reference's storage).  Layout (B, NC*4, H, 32 tokens):
+// the 32 tokens of a head's sub-block are contiguous, so a warp fetches its step with one 512-byte load.
+__device__ __forceinline__ size_t rec_index(const Args& a, int b, int c, int sub, int hd, int tl) {
+    return ((((size_t)b * a.NC + c) * kSteps + sub) * a.H + hd) * kSub + tl;
+}
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+struct BlockOut {   // what a sub-block walk hands back
+    cplx wh, xh;    // omega columns: Gamma[31,t] u~_t and -Gamma[31,t] x~_t
+    cplx ysum;      // pd u~_t + in-block read-out + W rho_z + W0 rho_r (before the |q|^-1 factor)
+};
+
+// The walk with explicit decay products (any a, including zeros): phases A (coefficients
+// cc[i] = a_t Gamma0[t,i] G_raw[t,i], Gamma0 built leftwards from the diagonal), B (substitution for
+// u~ = n u, x~ = n x) and C (in-block read-out; the correction is read before its step,
+// exact_correction.cu:90-94).  Reads G / P from tensor memory itself.
+template <bool kOutput>
+__device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, int J, int tl, cplx at, cplx W, cplx W0,
+                                             cplx vg, float be, float nt, cplx kz, cplx kr, cplx rz, cplx rr) {
+    const float bnn = be * nt * nt;
+    cplx S = at;   // inclusive suffix product
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        cplx dn = {__shfl_down_sync(0xffffffffu, S.r, o), __shfl_down_sync(0xffffffffu, S.i, o)};
+        if (tl + o < 32) S = cmul(S, dn);
+    }
+    cplx V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
+    if (tl == 31) V = {1.f, 0.f};
+    cplx cc[32];
+    {
+        cplx cur = {1.f, 0.f};
+#pragma unroll 1
+        for (int grp = 3; grp >= 0; grp--) {
+            if (grp < 3) {
+#pragma unroll
+                for (int k = 31; k >= 8; k--) cc[k] = cc[k - 8];
+            }
+            float g8[8];
+            tmem_ld8(tlane + kColG + 32 * (J & 1) + grp * 8, g8);
+#pragma unroll
+            for (int e = 7; e >= 0; e--) {
+                const int i = grp * 8 + e;
+                const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
+                const bool on = i < tl;
+                const cplx fg = cmul(at, cur);
+                cc[e] = {on ? fg.r * g8[e] : 0.f, on ? fg.i * g8[e] : 0.f};
+                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+            }
+        }
+    }
+    const cplx wkz = cmul(W, kz);
+    cplx cw = {nt * be * (vg.r - nt * wkz.r), nt * be * (vg.i - nt * wkz.i)};
+    cplx cx = {0.f, 0.f};
+    if (kOutput) {
+        const cplx wkr = cmul(W, kr);
+        cx = {nt * be * nt * wkr.r, nt * be * nt * wkr.i};
+    }
+#pragma unroll 1
+    for (int grp = 0; grp < 4; grp++) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int i = grp * 8 + e;
+            const float cr_ = bnn * cc[e].r, ci_ = bnn * cc[e].i;
+            const cplx uw = cshfl(cw, i);
+            cw.r -= cr_ * uw.r - ci_ * uw.i;
+            cw.i -= cr_ * uw.i + ci_ * uw.r;
+            if (kOutput) {
+                const cplx ux = cshfl(cx, i);
+                cx.r -= cr_ * ux.r - ci_ * ux.i;
+                cx.i -= cr_ * ux.i + ci_ * ux.r;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 24; k++) cc[k] = cc[k + 8];
+    }
+    BlockOut o;
+    o.wh = cmul(V, cw);
+    o.xh = {0.f, 0.f};
+    o.ysum = {0.f, 0.f};
+    if (kOutput) {
+        const cplx xv = cmul(V, cx);
+        o.xh = {-xv.r, -xv.i};
+        cplx yin = {0.f, 0.f};
+        float pd = 0.f;
+        cplx cur = {1.f, 0.f};
+#pragma unroll 1
+        for (int grp = 3; grp >= 0; grp--) {
+            float p8[8];
+            tmem_ld8(tlane + kColP + 32 * (J & 1) + grp * 8, p8);
+#pragma unroll
+            for (int e = 7; e >= 0; e--) {
+                const int i = grp * 8 + e;
+                const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
+                const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+                const bool on = i < tl;
+                pd = (i == tl) ? p8[e] : pd;
+                const cplx au = cmul(at, uw);
+                const cplx ee = cmul(cur, cplx{au.r - ux.r, au.i - ux.i});
+                const float pi = on ? p8[e] : 0.f;
+                yin.r += pi * ee.r;
+                yin.i += pi * ee.i;
+                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+            }
+        }
+        const cplx yz = cmul(W, rz), yr0 = cmul(W0, rr);
+        o.ysum = {pd * cw.r + yin.r + yz.r + yr0.r, pd * cw.i + yin.i + yz.i + yr0.i};
+    }
+    return o;
+}
+
+#define TC4_STAMP(idx) do { if (a.trace && blockIdx.x == 0 && tl == 0 && g < 16) a.trace[(g * 5 + J) * 16 + (idx)] = clock64(); } while (0)
+
+struct Tok {   // per-token quantities of one sub-block step, prepared one step ahead
+    cplx at, vg, W, W0, BP;   // a_t, vp-scaled value, inclusive / exclusive prefix products of a, block product
+    float be, sc;             // beta_t, sel_C gate
+    bool fast;
+};
+struct ItemPos {   // chunk c of heads h0 .. h0 + 3 of batch row b
+    int b, c, h0;
+};
+__device__ __forceinline__ ItemPos item_pos(const Args& a, int item) {
+    ItemPos p;
+    p.h0 = (item % a.HG) * 4;
+    p.c = (item / a.HG) % a.NC;
+    p.b = item / (a.HG * a.NC);
+    return p;
+}
+
+// Unpacks the token's record, forms the prefix products of a over the sub-block and chooses between the
+// scaled and the explicit walk.  Publishes a_t and the block product for step g (the block product is read
+// by all threads in the state hand-off).
+__device__ __forceinline__ Tok prepare(Smem& sm, const uint4& rec, int g, int J, int tl) {
+    Tok k;
+    k.at = {bf_lo(rec.x), bf_hi(rec.x)};
+    k.vg = {bf_lo(rec.y), bf_hi(rec.y)};
+    k.be = bf_lo(rec.z);
+    k.sc = bf_hi(rec.z);
+    sm.a[threadIdx.x] = *reinterpret_cast<const __nv_bfloat162*>(&rec.x);
+    cplx W = k.at;   // inclusive prefix product of a over the sub-block
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
+        if (tl >= o) W = cmul(W, up);
+    }
+    k.W = W;
+    k.W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
+    if (tl == 0) k.W0 = {1.f, 0.f};
+    k.BP = cshfl(W, 31);
+    if (tl == 31) sm.bp[g & 1][J] = make_float2(W.r, W.i);
+    __syncwarp();
+    if (tl == 0) mbar_arrive(&sm.bp_ready);
+    const float w2 = W.r * W.r + W.i * W.i;
+    k.fast = __all_sync(0xffffffffu, w2 >= 1e-36f && w2 <= 1e30f);
+    return k;
+}
+
 template <bool kOutput>
 __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
-    using T = __nv_bfloat16;
     volatile int* ab = &sm.abort_flag;
     const int t = threadIdx.x, J = t >> 5, tl = t & 31;
     const int H = a.H, L = a.L;
     const uint32_t tlane = sm.tmem_base + ((uint32_t)(J * 32) << 16);
+    const int n_items = ((int)blockIdx.x < a.items) ? (a.items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int NS = n_items * kSteps;
+    if (NS == 0) return;
     int code = 0;
     cplx Sz[4], Sr[4], gam[4];
-    int g = 0;   // flat step index
-    for (int item = blockIdx.x; item < a.items && !code; item += gridDim.x) {
-        const int h0 = (item % a.HG) * 4, c = (item / a.HG) % a.NC, b = item / (a.HG * a.NC);
-        const int hd = h0 + J;
-        const float lds = a.log_dt_scale[hd], freq = a.rope_freqs[hd];
-        const size_t unit0 = ((size_t)b * a.NC + c) * H + h0;   // workspace slot of head h0 (one pair per head)
-        // ---- states at the chunk start, column d = t of every head
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            Sz[u] = {0.f, 0.f};
-            Sr[u] = {0.f, 0.f};
-            gam[u] = {1.f, 0.f};
-            if (kOutput) {
-                const float* s = a.ws_state + (unit0 + u) * 2 * kD;
-                Sr[u] = {s[t], s[kD + t]};
-            }
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    ItemPos cur = item_pos(a, blockIdx.x), nxi = cur;
+    Tok tk;
+    {
+        const bool valid = cur.c * kC + tl < L;
+        const uint4 first = valid ? __ldg(a.rec + rec_index(a, cur.b, cur.c, 0, cur.h0 + J, tl)) : zero4;
+        tk = prepare(sm, first, 0, J, tl);
+    }
+    for (int g = 0; g < NS && !code; g++) {
+        const uint32_t ph = g & 1;
+        const int step = g & 3;
+        if (step == 0) {
+            if (g > 0) cur = nxi;
+            nxi = item_pos(a, (int)blockIdx.x + ((g >> 2) + 1) * (int)gridDim.x);
         }
-        for (int step = 0; step < kSteps && !code; step++, g++) {
-            const uint32_t ph = g & 1;
-            // ---- publish the states for kappa / rho of this step
+        const int l = cur.c * kC + step * kSub + tl, hd = cur.h0 + J;
+        const bool valid = l < L;
+        const size_t unit0 = ((size_t)cur.b * a.NC + cur.c) * H + cur.h0;   // workspace slot of head h0
+        if (step == 0) {   // states at the chunk start, column d = t of every head
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-                st_hi_lo(sm.s_tile, 8 * u + 0, t, Sz[u].r);
-                st_hi_lo(sm.s_tile, 8 * u + 2, t, Sz[u].i);
+                Sz[u] = {0.f, 0.f};
+                Sr[u] = {0.f, 0.f};
+                gam[u] = {1.f, 0.f};
                 if (kOutput) {
-                    st_hi_lo(sm.s_tile, 8 * u + 4, t, Sr[u].r);
-                    st_hi_lo(sm.s_tile, 8 * u + 6, t, Sr[u].i);
+                    const float* s = a.ws_state + (unit0 + u) * 2 * kD;
+                    Sr[u] = {s[t], s[kD + t]};
                 }
             }
-            fence_proxy_async();
+        }
+        // ---- publish the states for kappa / rho of this step
+        TC4_STAMP(11);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            st_hi_lo(sm.s_tile, 8 * u + 0, t, Sz[u].r);
+            st_hi_lo(sm.s_tile, 8 * u + 2, t, Sz[u].i);
+            if (kOutput) {
+                st_hi_lo(sm.s_tile, 8 * u + 4, t, Sr[u].r);
+                st_hi_lo(sm.s_tile, 8 * u + 6, t, Sr[u].i);
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (tl == 0) mbar_arrive(&sm.s_ready);
+        TC4_STAMP(0);
+        // ---- fetch the record of step g + 1 (the next item's first sub-block after this item's last)
+        uint4 rec = zero4;
+        if (g + 1 < NS) {
+            const ItemPos& np = (step + 1 < kSteps) ? cur : nxi;
+            const int nsub = (step + 1) & 3;
+            if (np.c * kC + nsub * kSub + tl < L) rec = __ldg(a.rec + rec_index(a, np.b, np.c, nsub, np.h0 + J, tl));
+        }
+        const cplx at = tk.at, vg = tk.vg, W = tk.W, W0 = tk.W0, BP = tk.BP;
+        const float be = tk.be;
+        TC4_STAMP(2);
+        // ---- Gram diagonals: |k_t|^-1, |q_t|^-1
+        if (!warp_wait(&sm.mma_gp, ph, ab)) { code = 13; break; }
+        tc_fence_after();
+        TC4_STAMP(3);
+        float gs[32], p[32];
+        float mt = 0.f, pd = 0.f;
+        if (kOutput) {
+            tmem_ld32(tlane + kColQQ, p);
+            float qd = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; i++) qd = (i == tl) ? p[i] : qd;
+            mt = rsqrtf(qd + kEps);
+        }
+        tmem_ld32(tlane + kColG + 32 * (J & 1), gs);
+        float gd = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) gd = (i == tl) ? gs[i] : gd;
+        const float nt = rsqrtf(gd + kEps);
+        const float bnn = be * nt * nt;
+        BlockOut o;
+        if (tk.fast) {
+            // coefficients of the real system, zero on and above the diagonal
+#pragma unroll
+            for (int i = 0; i < 32; i++) gs[i] = (i < tl) ? -bnn * gs[i] : 0.f;
+            if (kOutput) {
+                tmem_ld32(tlane + kColP + 32 * (J & 1), p);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    pd = (i == tl) ? p[i] : pd;
+                    p[i] = (i < tl) ? p[i] : 0.f;
+                }
+            }
             tc_fence_before();
             __syncwarp();
-            if (tl == 0) mbar_arrive(&sm.s_ready);
-            TC4_STAMP(0);
-            // ---- dynamics of this thread's token (dynamics_fused.cu:64-139; vp scale of block.py:194-195)
-            const int l = c * kC + step * kSub + tl;
-            const bool valid = l < L;
-            cplx at = {0.f, 0.f}, vg = {0.f, 0.f};
-            float be = 0.f, sc = 0.f;
-            if (valid) {
-                const size_t bl = (size_t)b * L + l;
-                const T* gr = a.gate_raw + bl * (size_t)(7 * H);
-                const float pos = (float)(l + a.pos0 + (b % a.segs) * L);
-                DynShared ds = dyn_shared<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), IO<T>::ld(gr + 2 * H + hd),
-                                                IO<T>::ld(gr + 3 * H + hd), IO<T>::ld(gr + 4 * H + hd),
-                                                IO<T>::ld(gr + 5 * H + hd), IO<T>::ld(gr + 6 * H + hd), lds, freq, pos,
-                                                a.dc);
-                float vp;
-                dyn_pair<true>(IO<T>::ld(gr + hd), IO<T>::ld(gr + H + hd), freq, pos, ds, at.r, at.i, vp);
-                at.r = bfr(at.r);
-                at.i = bfr(at.i);
-                vp = bfr(vp);
-                be = bfr(ds.beta);
-                sc = bfr(ds.sel_c);
-                const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v + (bl * H + hd) * 2);
-                vg.r = bfr(__low2float(v2) * vp);
-                vg.i = bfr(__high2float(v2) * vp);
-            }
-            sm.a[t] = __floats2bfloat162_rn(at.r, at.i);
-            cplx W = at, S = at;   // inclusive prefix / suffix products of a over the sub-block
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
-                cplx dn = {__shfl_down_sync(0xffffffffu, S.r, o), __shfl_down_sync(0xffffffffu, S.i, o)};
-                if (tl >= o) W = cmul(W, up);
-                if (tl + o < 32) S = cmul(S, dn);
-            }
-            cplx W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
-            cplx V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
-            if (tl == 0) W0 = {1.f, 0.f};
-            if (tl == 31) { V = {1.f, 0.f}; sm.bp[ph][J] = make_float2(W.r, W.i); }
-            __syncwarp();
-            if (tl == 0) mbar_arrive(&sm.bp_ready);
-            // ---- |q_t|^-1 from the Q tile row (swizzled 16-byte pieces)
-            float mt = 0.f;
-            if (kOutput) {
-                if (!warp_wait(&sm.full_q, ph, ab)) { code = 11; break; }
-                float qq = 0.f;
-#pragma unroll
-                for (int sl = 0; sl < 2; sl++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint4 r = *reinterpret_cast<const uint4*>(sm.q + sl * kSlab + t * 128 + ((j ^ (t & 7)) << 4));
-                        float f[8];
-                        unpack8(r, f);
-#pragma unroll
-                        for (int e = 0; e < 8; e++) qq += f[e] * f[e];
-                    }
-                mt = rsqrtf(qq + kEps);
-            }
-            TC4_STAMP(1);
-            // ---- diagonal block: P[t, :] into registers, G[t, :] streamed through phase A
-            if (!warp_wait(&sm.mma_gp, ph, ab)) { code = 13; break; }
+            if (tl == 0) mbar_arrive(&sm.gp_free);   // every read of this step's Gram blocks is done
+            if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
             tc_fence_after();
-            float p[32];
-            float pd = 0.f;
+            TC4_STAMP(4);
+            float k8[8], r8[8];
+            if (kOutput) tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
+            else tmem_ld8(tlane + kColKappa + 8 * J, k8);
+            const float w2 = W.r * W.r + W.i * W.i;
+            const float iden = __fdividef(1.f, w2);
+            const cplx viw = cmul(vg, cplx{W.r * iden, -W.i * iden});
+            cplx cw = {nt * be * (viw.r - nt * (k8[0] + k8[1])), nt * be * (viw.i - nt * (k8[2] + k8[3]))};
+            cplx cx = {0.f, 0.f}, accu = {0.f, 0.f}, accx = {0.f, 0.f};
+            if (kOutput) cx = {nt * be * nt * (k8[4] + k8[5]), nt * be * nt * (k8[6] + k8[7])};
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const cplx uw = cshfl(cw, i);
+                cw.r = fmaf(gs[i], uw.r, cw.r);
+                cw.i = fmaf(gs[i], uw.i, cw.i);
+                if (kOutput) {
+                    const cplx ux = cshfl(cx, i);
+                    cx.r = fmaf(gs[i], ux.r, cx.r);
+                    cx.i = fmaf(gs[i], ux.i, cx.i);
+                    accu.r = fmaf(p[i], uw.r, accu.r);
+                    accu.i = fmaf(p[i], uw.i, accu.i);
+                    accx.r = fmaf(p[i], ux.r, accx.r);
+                    accx.i = fmaf(p[i], ux.i, accx.i);
+                }
+            }
+            o.wh = cmul(BP, cw);
             if (kOutput) {
-                tmem_ld32(tlane + kColP, p);
+                const cplx xv = cmul(BP, cx);
+                o.xh = {-xv.r, -xv.i};
+                const cplx yl = cmul(W, cplx{r8[0] + r8[1] + pd * cw.r + accu.r, r8[2] + r8[3] + pd * cw.i + accu.i});
+                const cplx yc = cmul(W0, cplx{r8[4] + r8[5] - accx.r, r8[6] + r8[7] - accx.i});
+                o.ysum = {yl.r + yc.r, yl.i + yc.i};
+            }
+        } else {
+            if (kOutput) {
+                tmem_ld32(tlane + kColP + 32 * (J & 1), p);
 #pragma unroll
                 for (int i = 0; i < 32; i++) pd = (i == tl) ? p[i] : pd;
             }
-            // Phase A (no dependence on other lanes): coefficients of the unit-lower-triangular system for
-            // u~ = n u and x~ = n x:  u~_t = rhs_t - sum_{i<t} beta_t n_t^2 cc[i] u~_i,
-            // cc[i] = a_t Gamma0[t,i] G_raw[t,i],  Gamma0[t,i] = prod a_r, i < r <= t-1, built leftwards
-            // from the diagonal (0 for i >= t).  n_t = |k_t|^-1 comes from the Gram diagonal.
-            cplx cc[32];
-            float gd = 0.f;
-            {
-                cplx cur = {1.f, 0.f};
-#pragma unroll 1
-                for (int grp = 3; grp >= 0; grp--) {
-                    if (grp < 3) {
-#pragma unroll
-                        for (int k = 31; k >= 8; k--) cc[k] = cc[k - 8];
-                    }
-                    float g8[8];
-                    tmem_ld8(tlane + kColG + grp * 8, g8);
-#pragma unroll
-                    for (int e = 7; e >= 0; e--) {
-                        const int i = grp * 8 + e;
-                        const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
-                        const bool on = i < tl;
-                        gd = (i == tl) ? g8[e] : gd;
-                        const cplx fg = cmul(at, cur);
-                        cc[e] = {on ? fg.r * g8[e] : 0.f, on ? fg.i * g8[e] : 0.f};
-                        const cplx nx = cmul(cur, cplx{ai.x, ai.y});
-                        cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (tl == 0) mbar_arrive(&sm.gp_free);   // every read of this step's G / P / Q row is done
-            const float nt = rsqrtf(gd + kEps);      // |k_t|^-1
-            const float bnn = be * nt * nt;
-            TC4_STAMP(2);
-            // ---- kappa_t = k_t . z0 | r0, rho_t = q_t . z0 | r0 (raw rows; hi + lo parts summed)
             if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
             tc_fence_after();
-            TC4_STAMP(3);
-            float k8[8], r8[8];
-            if (kOutput) {
-                tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
-            } else {
-                tmem_ld8(tlane + kColKappa + 8 * J, k8);
-            }
-            const cplx wkz = cmul(W, cplx{k8[0] + k8[1], k8[2] + k8[3]});
-            cplx cw = {nt * be * (vg.r - nt * wkz.r), nt * be * (vg.i - nt * wkz.i)};
-            cplx cx = {0.f, 0.f};
-            if (kOutput) {
-                const cplx wkr = cmul(W, cplx{k8[4] + k8[5], k8[6] + k8[7]});
-                cx = {nt * be * nt * wkr.r, nt * be * nt * wkr.i};
-            }
-            // Phase B: the sequential substitution, eight columns per rolled iteration; the coefficient
-            // queue is rotated so that the unrolled body always reads slots 0..7.
-#pragma unroll 1
-            for (int grp = 0; grp < 4; grp++) {
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const int i = grp * 8 + e;
-                    const float cr_ = bnn * cc[e].r, ci_ = bnn * cc[e].i;
-                    const cplx uw = cshfl(cw, i);
-                    cw.r -= cr_ * uw.r - ci_ * uw.i;
-                    cw.i -= cr_ * uw.i + ci_ * uw.r;
-                    if (kOutput) {
-                        const cplx ux = cshfl(cx, i);
-                        cx.r -= cr_ * ux.r - ci_ * ux.i;
-                        cx.i -= cr_ * ux.i + ci_ * ux.r;
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 24; k++) cc[k] = cc[k + 8];
-            }
-            TC4_STAMP(4);
-            // ---- omega columns of the state update: z += sum_t V_t u~_t k_t, r -= sum_t V_t x~_t k_t
-            {
-                const cplx wh = cmul(V, cw);
-                st_hi_lo(sm.o_tile, 8 * J + 0, t, wh.r);
-                st_hi_lo(sm.o_tile, 8 * J + 2, t, wh.i);
-                if (kOutput) {
-                    const cplx xh = cmul(V, cx);
-                    st_hi_lo(sm.o_tile, 8 * J + 4, t, -xh.r);
-                    st_hi_lo(sm.o_tile, 8 * J + 6, t, -xh.i);
-                }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (tl == 0) mbar_arrive(&sm.omega_ready);
-            if (kOutput) {
-                // Phase C: in-block part of the read-out, sum_{i<t} P_raw[t,i] Gamma0[t,i] (a_t u~_i - x~_i);
-                // the correction is read before its step (exact_correction.cu:90-94)
-                cplx yin = {0.f, 0.f};
-                {
-                    cplx cur = {1.f, 0.f};
-#pragma unroll 1
-                    for (int grp = 3; grp >= 0; grp--) {
-#pragma unroll
-                        for (int e = 7; e >= 0; e--) {
-                            const int i = grp * 8 + e;
-                            const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
-                            const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
-                            const bool on = i < tl;
-                            const cplx au = cmul(at, uw);
-                            const cplx ee = cmul(cur, cplx{au.r - ux.r, au.i - ux.i});
-                            const float pi = on ? p[24 + e] : 0.f;
-                            yin.r += pi * ee.r;
-                            yin.i += pi * ee.i;
-                            const cplx nx = cmul(cur, cplx{ai.x, ai.y});
-                            cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
-                        }
-#pragma unroll
-                        for (int k = 31; k >= 8; k--) p[k] = p[k - 8];
-                    }
-                }
-                const cplx yz = cmul(W, cplx{r8[0] + r8[1], r8[2] + r8[3]});
-                const cplx yr0 = cmul(W0, cplx{r8[4] + r8[5], r8[6] + r8[7]});
-                float yr = mt * (pd * cw.r + yin.r + yz.r + yr0.r);
-                float yi = mt * (pd * cw.i + yin.i + yz.i + yr0.i);
-                if (a.shortcut_scale != 0.f) {   // block.py:202-208
-                    const float qk = mt * nt * pd;
-                    yr += a.shortcut_scale * qk * qk * vg.r;
-                    yi += a.shortcut_scale * qk * qk * vg.i;
-                }
-                if (valid) {
-                    __nv_bfloat162 o = __floats2bfloat162_rn(bfr(yr) * sc, bfr(yi) * sc);
-                    *reinterpret_cast<__nv_bfloat162*>(a.y + (((size_t)b * L + l) * H + hd) * 2) = o;
-                }
-            }
-            TC4_STAMP(5);
-            // ---- state hand-off: S <- BP S + K^T omega, column d = t of every head
-            if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 14; break; }
-            if (!warp_wait(&sm.mma_up, ph, ab)) { code = 15; break; }
-            tc_fence_after();
-            TC4_STAMP(6);
-            if (!kOutput || step + 1 < kSteps) {
-                float up[32];
-                tmem_ld32(tlane + kColUp, up);
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const cplx bpu = {sm.bp[ph][u].x, sm.bp[ph][u].y};
-                    const cplx nz = cmul(bpu, Sz[u]);
-                    Sz[u] = {nz.r + up[8 * u] + up[8 * u + 1], nz.i + up[8 * u + 2] + up[8 * u + 3]};
-                    if (kOutput) {
-                        const cplx nr = cmul(bpu, Sr[u]);
-                        Sr[u] = {nr.r + up[8 * u + 4] + up[8 * u + 5], nr.i + up[8 * u + 6] + up[8 * u + 7]};
-                    } else {
-                        gam[u] = cmul(bpu, gam[u]);
-                    }
-                }
-            }
+            float k8[8], r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (kOutput) tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
+            else tmem_ld8(tlane + kColKappa + 8 * J, k8);
+            o = robust_block<kOutput>(sm, tlane, J, tl, at, W, W0, vg, be, nt, cplx{k8[0] + k8[1], k8[2] + k8[3]},
+                                      cplx{k8[4] + k8[5], k8[6] + k8[7]}, cplx{r8[0] + r8[1], r8[2] + r8[3]},
+                                      cplx{r8[4] + r8[5], r8[6] + r8[7]});
             tc_fence_before();
-            TC4_STAMP(7);
+            __syncwarp();
+            if (tl == 0) mbar_arrive(&sm.gp_free);
         }
-        if (!kOutput && !code) {
+        TC4_STAMP(5);
+        // ---- omega columns of the state update: z += sum_t Gamma[31,t] u~_t k_t, r -= sum_t Gamma[31,t] x~_t k_t
+        st_hi_lo(sm.o_tile, 8 * J + 0, t, o.wh.r);
+        st_hi_lo(sm.o_tile, 8 * J + 2, t, o.wh.i);
+        if (kOutput) {
+            st_hi_lo(sm.o_tile, 8 * J + 4, t, o.xh.r);
+            st_hi_lo(sm.o_tile, 8 * J + 6, t, o.xh.i);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (tl == 0) mbar_arrive(&sm.omega_ready);
+        if (kOutput) {
+            float yr = mt * o.ysum.r, yi = mt * o.ysum.i;
+            if (a.shortcut_scale != 0.f) {   // block.py:202-208
+                const float qk = mt * nt * pd;
+                yr += a.shortcut_scale * qk * qk * vg.r;
+                yi += a.shortcut_scale * qk * qk * vg.i;
+            }
+            if (valid) {
+                __nv_bfloat162 ov = __floats2bfloat162_rn(bfr(yr) * tk.sc, bfr(yi) * tk.sc);
+                *reinterpret_cast<__nv_bfloat162*>(a.y + (((size_t)cur.b * L + l) * H + hd) * 2) = ov;
+            }
+        }
+        TC4_STAMP(1);
+        // ---- the next step's token while the state-update UMMA runs.  This step's block products are waited
+        // for first: prepare() arrives on the same barrier for the next step, and a wait must never be two
+        // phases behind its barrier.
+        if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 14; break; }
+        if (g + 1 < NS) tk = prepare(sm, rec, g + 1, J, tl);
+        TC4_STAMP(8);
+        // ---- state hand-off: S <- BP S + K^T omega, column d = t of every head
+        if (!warp_wait(&sm.mma_up, ph, ab)) { code = 15; break; }
+        tc_fence_after();
+        TC4_STAMP(6);
+        if (!kOutput || step + 1 < kSteps) {
+            float up[32];
+            tmem_ld32(tlane + kColUp, up);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const cplx bpu = {sm.bp[ph][u].x, sm.bp[ph][u].y};
+                const cplx nz = cmul(bpu, Sz[u]);
+                Sz[u] = {nz.r + up[8 * u] + up[8 * u + 1], nz.i + up[8 * u + 2] + up[8 * u + 3]};
+                if (kOutput) {
+                    const cplx nr = cmul(bpu, Sr[u]);
+                    Sr[u] = {nr.r + up[8 * u + 4] + up[8 * u + 5], nr.i + up[8 * u + 6] + up[8 * u + 7]};
+                } else {
+                    gam[u] = cmul(bpu, gam[u]);
+                }
+            }
+        }
+        tc_fence_before();
+        TC4_STAMP(7);
+        if (!kOutput && step + 1 == kSteps) {
             // the carry pass consumes these as the reference's bf16 cum_A[:, -1] / local_h[:, -1]
 #pragma unroll
             for (int u = 0; u < 4; u++) {
@@ -550,9 +771,12 @@ scan_tc4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 
     if (warp < 4) {
         compute<kOutput>(sm, a);
-    } else if (threadIdx.x == 128) {
-        prefetch_tmap(&tmK);
-        if (kOutput) prefetch_tmap(&tmQ);
+    } else {
+        if (threadIdx.x == 128) {
+            prefetch_tmap(&tmK);
+            if (kOutput) prefetch_tmap(&tmQ);
+        }
+        __syncwarp();
         producer<kOutput>(sm, &tmK, &tmQ, a);
     }
     tc_fence_before();
@@ -561,6 +785,48 @@ scan_tc4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         __syncwarp();
         tmem_dealloc(sm.tmem_base, kTmemCols);
     }
+}
+
+// ------------------------------------------------------------------------------------------
+// Dynamics pre-pass: one thread per (token, head), heads fastest (the gate rows are read coalesced).
+// dynamics_fused.cu:64-139 and the vp scale of block.py:194-195, every result rounded to bf16 like the
+// reference's stores.  Both scan passes read the 16-byte records instead of repeating the transcendental
+// chain inside their sequential walks.
+// ------------------------------------------------------------------------------------------
+struct DynArgs {
+    const __nv_bfloat16 *v, *gate_raw;
+    const float *log_dt_scale, *rope_freqs;
+    uint4* rec;
+    DynConsts dc;
+    int B, L, H, NC, pos0, segs;
+};
+__global__ void __launch_bounds__(256) tc4_dynamics_kernel(const DynArgs a) {
+    using T = __nv_bfloat16;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)a.B * a.L * a.H;
+    if (idx >= total) return;
+    const int hd = (int)(idx % a.H);
+    const long long bl = idx / a.H;
+    const int l = (int)(bl % a.L), b = (int)(bl / a.L);
+    const int H = a.H;
+    const T* gr = a.gate_raw + (size_t)bl * (size_t)(7 * H);
+    const float lds = a.log_dt_scale[hd], freq = a.rope_freqs[hd];
+    const float pos = (float)(l + a.pos0 + (b % a.segs) * a.L);
+    const float g0 = IO<T>::ld(gr + hd), g1 = IO<T>::ld(gr + H + hd);
+    DynShared ds = dyn_shared<true>(g0, g1, IO<T>::ld(gr + 2 * H + hd), IO<T>::ld(gr + 3 * H + hd),
+                                    IO<T>::ld(gr + 4 * H + hd), IO<T>::ld(gr + 5 * H + hd), IO<T>::ld(gr + 6 * H + hd),
+                                    lds, freq, pos, a.dc);
+    float ar, ai, vp;
+    dyn_pair<true>(g0, g1, freq, pos, ds, ar, ai, vp);
+    vp = bfr(vp);
+    const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v + ((size_t)bl * H + hd) * 2);
+    uint4 r;
+    r.x = pack2(ar, ai);
+    r.y = pack2(__low2float(v2) * vp, __high2float(v2) * vp);
+    r.z = pack2(ds.beta, ds.sel_c);
+    r.w = 0u;
+    const int c = l / kC, sub = (l % kC) / kSub, tl = l % kSub;
+    a.rec[((((size_t)b * a.NC + c) * kSteps + sub) * H + hd) * kSub + tl] = r;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -605,13 +871,31 @@ bool scan_tc4_supported(int D, int N, int C, int H, int dtype) {
     return dtype == CDSSM_BF16 && N == 2 && D == tc4::kD && C == tc4::kC && H % 4 == 0;
 }
 
+size_t scan_tc4_record_bytes(int B, int L, int H) {
+    const size_t NC = ((size_t)L + tc4::kC - 1) / tc4::kC;
+    return (size_t)B * NC * tc4::kC * H * sizeof(uint4);
+}
+
+// Dynamics pre-pass: fills rec (scan_tc4_record_bytes bytes) for both scan passes.
+int scan_tc4_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
+                      void* rec, const DynConsts& dc, int B, int L, int H, int pos0, int segs, cudaStream_t st) {
+    tc4::DynArgs d;
+    d.v = static_cast<const __nv_bfloat16*>(v);
+    d.gate_raw = static_cast<const __nv_bfloat16*>(gate_raw);
+    d.log_dt_scale = log_dt_scale; d.rope_freqs = rope_freqs;
+    d.rec = static_cast<uint4*>(rec);
+    d.dc = dc;
+    d.B = B; d.L = L; d.H = H; d.NC = (L + tc4::kC - 1) / tc4::kC; d.pos0 = pos0; d.segs = segs;
+    const long long total = (long long)B * L * H;
+    tc4::tc4_dynamics_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d);
+    return check_launch();
+}
+
 // One pass of the four-chain tensor-core scan over every chunk.  output = false: local pass (fills
 // ws_state / ws_gamma for the carry pass); output = true: reads the carries from ws_state, writes y.
 // status: one int in device memory, set by a bounded wait that ran out (not cleared here).
-int scan_tc4_pass(bool output, const void* q, const void* k, const void* v, const void* gate_raw,
-                  const float* log_dt_scale, const float* rope_freqs, float* ws_gamma, float* ws_state, void* y,
-                  int* status, const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
-                  cudaStream_t st) {
+int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, float* ws_gamma, float* ws_state,
+                  void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st) {
     using namespace tc4;
     CUtensorMap tmK, tmQ;
     if (!make_tile_map(&tmK, k, B, L, H) || !make_tile_map(&tmQ, output ? q : k, B, L, H)) return CDSSM_ERR_CUDA;
@@ -629,14 +913,12 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* v, cons
         attr = true;
     }
     Args a;
-    a.v = static_cast<const __nv_bfloat16*>(v);
-    a.gate_raw = static_cast<const __nv_bfloat16*>(gate_raw);
-    a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs;
+    a.rec = static_cast<const uint4*>(rec);
     a.ws_gamma = ws_gamma; a.ws_state = ws_state;
     a.y = static_cast<__nv_bfloat16*>(y);
     a.status = status; a.trace = g_trace;
-    a.dc = dc; a.shortcut_scale = shortcut_scale;
-    a.B = B; a.L = L; a.H = H; a.NC = (L + kC - 1) / kC; a.pos0 = pos0; a.segs = segs;
+    a.shortcut_scale = shortcut_scale;
+    a.B = B; a.L = L; a.H = H; a.NC = (L + kC - 1) / kC;
     a.HG = H / 4;
     const long long items = (long long)B * a.NC * a.HG;
     if (items > 0x7fffffff / 8) return CDSSM_ERR_UNSUPPORTED;
