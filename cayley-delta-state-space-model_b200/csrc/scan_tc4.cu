@@ -27,6 +27,7 @@
 // (W, W0: inclusive / exclusive prefix products of a inside the sub-block, V: exclusive suffix.)
 #include "cdssm_common.cuh"
 #include "sm100_ptx.cuh"
+#include <cstdlib>
 
 namespace cdssm {
 using namespace sm100;
@@ -62,6 +63,7 @@ struct Args {
     __nv_bfloat16* y;
     int* status;
     long long* trace;
+    int trace_g0, trace_block;   // debugging: first traced step and the traced block
     float shortcut_scale;
     int B, L, H, NC;
     int HG, items;               // head groups of four; items = B * NC * HG (one chunk of four heads each)
@@ -224,7 +226,7 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
     bool k_ok = false, q_ok = !kOutput;
     uint64_t last = global_ns();
     uint32_t idle = 0;
-#define TC4_PSTAMP(n, idx) do { if (a.trace && (threadIdx.x & 31) == 0 && blockIdx.x == 0 && (n) < 16) a.trace[((n) * 5 + 4) * 16 + (idx)] = clock64(); } while (0)
+#define TC4_PSTAMP(n, idx) do { if (a.trace && (threadIdx.x & 31) == 0 && blockIdx.x == a.trace_block && (n) >= a.trace_g0 && (n) < a.trace_g0 + 16) a.trace[(((n) - a.trace_g0) * 5 + 4) * 16 + (idx)] = clock64(); } while (0)
     auto par = [](int n) { return (uint32_t)(n & 1); };
     // Tasks in order of urgency: the state update and kappa / rho sit on the compute warps' critical path,
     // the tile loads and the Gram blocks of the NEXT step do not; the Gram blocks are issued one head at a
@@ -372,15 +374,19 @@ struct BlockOut {   // what a sub-block walk hands back
 // u~ = n u, x~ = n x) and C (in-block read-out; the correction is read before its step,
 // exact_correction.cu:90-94).  Reads G / P from tensor memory itself.
 template <bool kOutput>
-__device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, int J, int tl, cplx at, cplx W, cplx W0,
-                                             cplx vg, float be, float nt, cplx kz, cplx kr, cplx rz, cplx rr) {
+__device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, int J, int tl, cplx at, cplx vg, float be,
+                                             float nt, cplx kz, cplx kr, cplx rz, cplx rr) {
     const float bnn = be * nt * nt;
-    cplx S = at;   // inclusive suffix product
+    cplx W = at, S = at;   // inclusive prefix / suffix products of a over the sub-block
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
+        cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
         cplx dn = {__shfl_down_sync(0xffffffffu, S.r, o), __shfl_down_sync(0xffffffffu, S.i, o)};
+        if (tl >= o) W = cmul(W, up);
         if (tl + o < 32) S = cmul(S, dn);
     }
+    cplx W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
+    if (tl == 0) W0 = {1.f, 0.f};
     cplx V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
     if (tl == 31) V = {1.f, 0.f};
     cplx cc[32];
@@ -467,11 +473,14 @@ __device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, in
     return o;
 }
 
-#define TC4_STAMP(idx) do { if (a.trace && blockIdx.x == 0 && tl == 0 && g < 16) a.trace[(g * 5 + J) * 16 + (idx)] = clock64(); } while (0)
+#define TC4_STAMP(idx) do { if (a.trace && blockIdx.x == a.trace_block && tl == 0 && g >= a.trace_g0 && g < a.trace_g0 + 16) a.trace[((g - a.trace_g0) * 5 + J) * 16 + (idx)] = clock64(); } while (0)
 
 struct Tok {   // per-token quantities of one sub-block step, prepared one step ahead
-    cplx at, vg, W, W0, BP;   // a_t, vp-scaled value, inclusive / exclusive prefix products of a, block product
-    float be, sc;             // beta_t, sel_C gate
+    cplx at, vg;        // a_t, vp-scaled value
+    cplx viw;           // vg / D_t
+    cplx D, D0;         // scaling of token t (see prepare) and of token t - 1
+    cplx R, D31;        // reference product W_15 and D of the last token: W_31 = D31 R
+    float be, sc;       // beta_t, sel_C gate
     bool fast;
 };
 struct ItemPos {   // chunk c of heads h0 .. h0 + 3 of batch row b
@@ -485,9 +494,12 @@ __device__ __forceinline__ ItemPos item_pos(const Args& a, int item) {
     return p;
 }
 
-// Unpacks the token's record, forms the prefix products of a over the sub-block and chooses between the
-// scaled and the explicit walk.  Publishes a_t and the block product for step g (the block product is read
-// by all threads in the state hand-off).
+// Unpacks the token's record and forms the decay scalings of the sub-block.  The scaled walk only needs
+// ratios W_t / W_i of the prefix products W_t = a_0 ... a_t, so they are taken relative to the middle of the
+// sub-block, D_t = W_t / W_15: lanes 0-15 hold the suffix product a_{t+1} ... a_15 = 1 / D_t, lanes 16-31 the
+// prefix product a_16 ... a_t = D_t, and neither half leaves the float range unless one half alone decays by
+// more than 1e-30 (then, or with the zero padding behind the sequence end, the explicit walk is taken).
+// Publishes a_t and the block product W_31 for step g (read by all threads in the state hand-off).
 __device__ __forceinline__ Tok prepare(Smem& sm, const uint4& rec, int g, int J, int tl) {
     Tok k;
     k.at = {bf_lo(rec.x), bf_hi(rec.x)};
@@ -495,21 +507,40 @@ __device__ __forceinline__ Tok prepare(Smem& sm, const uint4& rec, int g, int J,
     k.be = bf_lo(rec.z);
     k.sc = bf_hi(rec.z);
     sm.a[threadIdx.x] = *reinterpret_cast<const __nv_bfloat162*>(&rec.x);
-    cplx W = k.at;   // inclusive prefix product of a over the sub-block
+    const bool lo = tl < 16;
+    // lanes < 16: exclusive suffix product inside the first half; lanes >= 16: inclusive prefix inside the second
+    cplx X = k.at;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
-        if (tl >= o) W = cmul(W, up);
+    for (int o = 1; o < 16; o <<= 1) {
+        const cplx other = cshfl(X, lo ? tl + o : tl - o);
+        const bool take = lo ? (tl + o < 16) : (tl - o >= 16);
+        if (take) X = cmul(X, other);
     }
-    k.W = W;
-    k.W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
-    if (tl == 0) k.W0 = {1.f, 0.f};
-    k.BP = cshfl(W, 31);
-    if (tl == 31) sm.bp[g & 1][J] = make_float2(W.r, W.i);
+    const cplx incl0 = cshfl(X, 0);              // a_0 ... a_15 = W_15
+    cplx E = cshfl(X, tl + 1);                   // first half: exclusive suffix = inclusive suffix of lane t + 1
+    if (tl == 15) E = {1.f, 0.f};
+    if (!lo) E = X;
+    // E: 1 / D_t (first half) or D_t (second half); one complex reciprocal gives the other
+    const float m = fmaxf(fabsf(E.r), fabsf(E.i));
+    const bool in_range = m >= 1e-30f && m <= 1e30f;
+    const float sc1 = __fdividef(1.f, m);
+    const cplx En = {E.r * sc1, E.i * sc1};
+    const float q = __fdividef(sc1, En.r * En.r + En.i * En.i);
+    const cplx Einv = {En.r * q, -En.i * q};
+    k.D = lo ? Einv : E;
+    const cplx Dinv = lo ? E : Einv;
+    k.viw = cmul(k.vg, Dinv);
+    k.R = incl0;
+    k.D31 = cshfl(k.D, 31);
+    k.D0 = cshfl(k.D, tl - 1);                   // lane 0 never uses it (W0 = 1 there)
+    const float mr = fmaxf(fabsf(incl0.r), fabsf(incl0.i));
+    k.fast = __all_sync(0xffffffffu, in_range && mr >= 1e-30f && mr <= 1e30f);
+    if (tl == 31) {
+        const cplx bp = cmul(k.D, incl0);        // W_31
+        sm.bp[g & 1][J] = make_float2(bp.r, bp.i);
+    }
     __syncwarp();
     if (tl == 0) mbar_arrive(&sm.bp_ready);
-    const float w2 = W.r * W.r + W.i * W.i;
-    k.fast = __all_sync(0xffffffffu, w2 >= 1e-36f && w2 <= 1e30f);
     return k;
 }
 
@@ -577,7 +608,7 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
             const int nsub = (step + 1) & 3;
             if (np.c * kC + nsub * kSub + tl < L) rec = __ldg(a.rec + rec_index(a, np.b, np.c, nsub, np.h0 + J, tl));
         }
-        const cplx at = tk.at, vg = tk.vg, W = tk.W, W0 = tk.W0, BP = tk.BP;
+        const cplx at = tk.at, vg = tk.vg;
         const float be = tk.be;
         TC4_STAMP(2);
         // ---- Gram diagonals: |k_t|^-1, |q_t|^-1
@@ -621,12 +652,13 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
             float k8[8], r8[8];
             if (kOutput) tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
             else tmem_ld8(tlane + kColKappa + 8 * J, k8);
-            const float w2 = W.r * W.r + W.i * W.i;
-            const float iden = __fdividef(1.f, w2);
-            const cplx viw = cmul(vg, cplx{W.r * iden, -W.i * iden});
-            cplx cw = {nt * be * (viw.r - nt * (k8[0] + k8[1])), nt * be * (viw.i - nt * (k8[2] + k8[3]))};
+            const cplx rkz = cmul(tk.R, cplx{k8[0] + k8[1], k8[2] + k8[3]});
+            cplx cw = {nt * be * (tk.viw.r - nt * rkz.r), nt * be * (tk.viw.i - nt * rkz.i)};
             cplx cx = {0.f, 0.f}, accu = {0.f, 0.f}, accx = {0.f, 0.f};
-            if (kOutput) cx = {nt * be * nt * (k8[4] + k8[5]), nt * be * nt * (k8[6] + k8[7])};
+            if (kOutput) {
+                const cplx rkr = cmul(tk.R, cplx{k8[4] + k8[5], k8[6] + k8[7]});
+                cx = {nt * be * nt * rkr.r, nt * be * nt * rkr.i};
+            }
 #pragma unroll
             for (int i = 0; i < 32; i++) {
                 const cplx uw = cshfl(cw, i);
@@ -642,12 +674,15 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
                     accx.i = fmaf(p[i], ux.i, accx.i);
                 }
             }
-            o.wh = cmul(BP, cw);
+            o.wh = cmul(tk.D31, cw);
             if (kOutput) {
-                const cplx xv = cmul(BP, cx);
+                const cplx xv = cmul(tk.D31, cx);
                 o.xh = {-xv.r, -xv.i};
-                const cplx yl = cmul(W, cplx{r8[0] + r8[1] + pd * cw.r + accu.r, r8[2] + r8[3] + pd * cw.i + accu.i});
-                const cplx yc = cmul(W0, cplx{r8[4] + r8[5] - accx.r, r8[6] + r8[7] - accx.i});
+                const cplx rz = cmul(tk.R, cplx{r8[0] + r8[1], r8[2] + r8[3]});
+                const cplx rr = cmul(tk.R, cplx{r8[4] + r8[5], r8[6] + r8[7]});
+                const cplx yl = cmul(tk.D, cplx{rz.r + pd * cw.r + accu.r, rz.i + pd * cw.i + accu.i});
+                cplx yc = cmul(tk.D0, cplx{rr.r - accx.r, rr.i - accx.i});
+                if (tl == 0) yc = {r8[4] + r8[5], r8[6] + r8[7]};   // W0 = 1: the carried correction itself
                 o.ysum = {yl.r + yc.r, yl.i + yc.i};
             }
         } else {
@@ -661,7 +696,7 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
             float k8[8], r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (kOutput) tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
             else tmem_ld8(tlane + kColKappa + 8 * J, k8);
-            o = robust_block<kOutput>(sm, tlane, J, tl, at, W, W0, vg, be, nt, cplx{k8[0] + k8[1], k8[2] + k8[3]},
+            o = robust_block<kOutput>(sm, tlane, J, tl, at, vg, be, nt, cplx{k8[0] + k8[1], k8[2] + k8[3]},
                                       cplx{k8[4] + k8[5], k8[6] + k8[7]}, cplx{r8[0] + r8[1], r8[2] + r8[3]},
                                       cplx{r8[4] + r8[5], r8[6] + r8[7]});
             tc_fence_before();
@@ -917,6 +952,11 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
     a.ws_gamma = ws_gamma; a.ws_state = ws_state;
     a.y = static_cast<__nv_bfloat16*>(y);
     a.status = status; a.trace = g_trace;
+    a.trace_g0 = 0; a.trace_block = 0;
+    if (g_trace) {
+        if (const char* e = getenv("CDSSM_TC4_TRACE_G0")) a.trace_g0 = atoi(e);
+        if (const char* e = getenv("CDSSM_TC4_TRACE_BLOCK")) a.trace_block = atoi(e);
+    }
     a.shortcut_scale = shortcut_scale;
     a.B = B; a.L = L; a.H = H; a.NC = (L + kC - 1) / kC;
     a.HG = H / 4;
