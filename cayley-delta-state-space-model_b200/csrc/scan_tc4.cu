@@ -374,7 +374,7 @@ struct BlockOut {   // what a sub-block walk hands back
 // u~ = n u, x~ = n x) and C (in-block read-out; the correction is read before its step,
 // exact_correction.cu:90-94).  Reads G / P from tensor memory itself.
 template <bool kOutput>
-__device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, int J, int tl, cplx at, cplx vg, float be,
+__device__ __forceinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, int J, int tl, cplx at, cplx vg, float be,
                                              float nt, cplx kz, cplx kr, cplx rz, cplx rr) {
     const float bnn = be * nt * nt;
     cplx W = at, S = at;   // inclusive prefix / suffix products of a over the sub-block
@@ -389,15 +389,13 @@ __device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, in
     if (tl == 0) W0 = {1.f, 0.f};
     cplx V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
     if (tl == 31) V = {1.f, 0.f};
+    // cc is indexed with run-time group numbers on purpose: it lives in local memory, so this rarely taken
+    // walk does not compete for registers with the scaled walk it is inlined next to.
     cplx cc[32];
     {
         cplx cur = {1.f, 0.f};
 #pragma unroll 1
         for (int grp = 3; grp >= 0; grp--) {
-            if (grp < 3) {
-#pragma unroll
-                for (int k = 31; k >= 8; k--) cc[k] = cc[k - 8];
-            }
             float g8[8];
             tmem_ld8(tlane + kColG + 32 * (J & 1) + grp * 8, g8);
 #pragma unroll
@@ -406,7 +404,7 @@ __device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, in
                 const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
                 const bool on = i < tl;
                 const cplx fg = cmul(at, cur);
-                cc[e] = {on ? fg.r * g8[e] : 0.f, on ? fg.i * g8[e] : 0.f};
+                cc[i] = {on ? fg.r * g8[e] : 0.f, on ? fg.i * g8[e] : 0.f};
                 const cplx nx = cmul(cur, cplx{ai.x, ai.y});
                 cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
             }
@@ -424,7 +422,7 @@ __device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, in
 #pragma unroll
         for (int e = 0; e < 8; e++) {
             const int i = grp * 8 + e;
-            const float cr_ = bnn * cc[e].r, ci_ = bnn * cc[e].i;
+            const float cr_ = bnn * cc[i].r, ci_ = bnn * cc[i].i;
             const cplx uw = cshfl(cw, i);
             cw.r -= cr_ * uw.r - ci_ * uw.i;
             cw.i -= cr_ * uw.i + ci_ * uw.r;
@@ -434,8 +432,6 @@ __device__ __noinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, in
                 cx.i -= cr_ * ux.i + ci_ * ux.r;
             }
         }
-#pragma unroll
-        for (int k = 0; k < 24; k++) cc[k] = cc[k + 8];
     }
     BlockOut o;
     o.wh = cmul(V, cw);
