@@ -313,7 +313,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--segments", type=int, default=0, help="cfg4: segments per sequence over all GPUs (default: the workload's)")
-    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (2 = the single-pass tcgen05/TMA kernel)")
+    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (2 = the single-pass tcgen05/TMA kernel, 64 = the four-chain tcgen05/TMA passes)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -437,7 +437,7 @@ def main():
             if dist is not None:
                 dist.all_reduce(t3, op=dist.ReduceOp.MAX)
             extra["segment_passes_ms"] = {"summary": float(t3[0]), "exposed_handoff": float(t3[1]), "scan": float(t3[2])}
-        elif not (args.flags & 2):
+        elif not (args.flags & (2 | 64)):
             # the dominant kernel alone: the output pass = whole step minus (local pass + carry pass)
             def summary_step():
                 return ops.scan_summary(k, v, gate, lds, rope, *consts, H, N, C)
@@ -456,10 +456,12 @@ def main():
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic", "config": workload_config(args.workload, w),
                 "clocks": clocks.summary(t_begin, t_end), "e2e": e2e,
-                "gpu_launches": (1 if args.flags & 2 else 3) * args.steps,
+                "gpu_launches": (1 if args.flags & 2 else 4 if args.flags & 64 else 3) * args.steps,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                              "kernel": ("scan_tc_kernel (single pass)" if args.flags & 2 else
+                                        "the whole step (tc4_dynamics + scan_tc4 local pass + scan_carry + scan_tc4 "
+                                        "output pass)" if args.flags & 64 else
                                         "the whole step (scan_walk local pass + scan_carry + scan_walk output pass)"),
                              "algorithmic_bytes_per_launch": abytes}}
         if "summary_ms" in extra:

@@ -87,3 +87,46 @@ def test_tc4_flag_rejects_unsupported_sizes(ops, orc):
     inp = orc.make_inputs(1, 3, 128, 128, N=2, seed=1, bf16=True)   # H not a multiple of 4
     with pytest.raises(RuntimeError):
         run_fused(ops, inp, torch.bfloat16, 2, 128, flags=ops.TENSOR_CORE4)
+
+
+def test_tc4_segmented_scan_equals_unsegmented(ops, orc):
+    """Sequence segments as extra batch rows: the tensor-core output pass on the CUDA-core summary."""
+    from util import const_args, to_dev
+    B, H, L, S = 1, 4, 1024, 4
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=3, bf16=True)
+    h0 = np.random.default_rng(3).standard_normal((B, H, N, D)).astype(np.float32) * 0.3
+    d = lambda x: to_dev(x, torch.bfloat16)
+    f = lambda x: to_dev(x, torch.float32)
+    args = (d(inp["q"]), d(inp["k"]), d(inp["v"]), d(inp["gate_raw"]), f(inp["log_dt_scale"]), f(inp["rope_freqs"]),
+            *const_args(inp["consts"]), H, N, C, f(h0))
+    y, fin = ops.scan_fused(*args, shortcut_scale=0.4, pos0=7)
+    ys, fs = ops.scan_fused_long(*args, segments=S, shortcut_scale=0.4, pos0=7, flags=ops.TENSOR_CORE4)
+    assert ops.scan_fused_status() == 0
+    assert rel_err(to_np(ys), to_np(y)) <= 2.0 ** -7
+    assert rel_err(to_np(fs), to_np(fin)) <= 2.0 ** -9
+
+
+@pytest.mark.parametrize("alpha_gate", [None, 2.0])
+def test_tc4_strong_decay(ops, orc, alpha_gate):
+    """Gates pushed towards strong decay over 200 tokens.  alpha_gate None: half-sub-block decay products down
+    to about 1e-27, still inside the range of the scaled walk (scalings up to 1e27); alpha_gate 2.0: down to
+    about 1e-48, where the kernel falls back to the explicit walk.  Both must agree with the CUDA-core
+    kernels and the oracle."""
+    B, H, L = 1, 4, 512
+    inp = _inputs(orc, B, H, L, seed=11)
+    g = inp["gate_raw"].copy()
+    g[:, 100:300, 6 * H:7 * H] += 8.0            # r gate: exponent of the decay magnitude at its maximum
+    if alpha_gate is None:
+        g[:, 100:300, 0:H] += 4.0                # decay-rate pre-activation
+    else:
+        g[:, 100:300, 0:H] = alpha_gate
+        g[:, 100:300, H:2 * H] = 0.0             # no rotation: the Cayley map gets closest to zero
+    inp["gate_raw"] = orc.bf16_round(g)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.TENSOR_CORE4)
+    assert ops.scan_fused_status() == 0
+    ys, fs = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.FORCE_SIMT)
+    wy13, _ = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE)
+    assert np.isfinite(to_np(y)).all()
+    assert rel_err(to_np(y), wy13) <= BF16_TOL / 2
+    assert rel_err(to_np(y), to_np(ys)) <= BF16_TOL / 2
+    assert np.abs(to_np(fin) - to_np(fs)).max() <= 2e-2 * max(np.abs(to_np(fs)).max(), 1e-3)
