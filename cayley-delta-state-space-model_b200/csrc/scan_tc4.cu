@@ -38,7 +38,7 @@ constexpr int kC = 128, kD = 128, kSub = 32, kSteps = kC / kSub;
 constexpr int kThreads = 160;
 constexpr uint32_t kTmemCols = 256;
 // G and P: 64 columns each - a pair of heads per UMMA, a thread reads the 32 columns of its own head
-constexpr uint32_t kColG = 0, kColP = 64, kColQQ = 128, kColKappa = 160, kColRho = 192, kColUp = 224;
+constexpr uint32_t kColG = 0, kColP = 64, kColKappa = 128, kColRho = 160, kColUp = 192;
 constexpr uint32_t kSlab = 128 * 128;          // 64 bf16 columns x 128 rows
 constexpr uint32_t kTile = 2 * kSlab;          // 32 KB
 constexpr uint32_t kSmallSlab = 32 * 128;      // 32-row operand tiles: 4 KB per 64 columns
@@ -274,9 +274,10 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
             // the K stage of step n is free once its state update has completed
             if (i_lk < NS) { TC4_PSTAMP(i_lk, 5); load_tile(sm.k[i_lk & 1], tmK, &sm.full_k[i_lk & 1], i_lk); pend_k[i_lk & 1] = true; }
             i_lk++; progress = true;
-        } else if (kOutput && i_lq <= i_kr && i_lq <= NS && warp_test(&sm.mma_kr, par(i_lq - 1))) {
+        } else if (kOutput && i_lq <= i_kr && i_lq <= NS && warp_test(&sm.mma_kr, par(i_lq - 1)) &&
+                   warp_test(&sm.gp_free, par(i_lq - 1))) {
             // Q tile of step n is free once its UMMAs have completed (mma_kr is committed after mma_gp of the
-            // same step, so it covers both); the compute warps never read it themselves
+            // same step, so it covers both) and the compute warps have taken |q| from it (before gp_free)
             if (i_lq < NS) { TC4_PSTAMP(i_lq, 4); load_tile(sm.q, tmQ, &sm.full_q, i_lq); pend_q = true; }
             i_lq++; progress = true;
         } else if (i_gp < NS) {   // diagonal Gram blocks of step i_gp, head gp_u
@@ -286,22 +287,16 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
             if (k_ok && q_ok && (n == 0 || gp_u > 0 || warp_test(&sm.gp_free, par(n - 1)))) {
                 if (gp_u == 0) { tc_fence_after(); TC4_PSTAMP(i_gp, 0); }
                 // One pair of heads per visit: G and P of the pair as one N = 64 UMMA each (the pair's 64 lanes
-                // enabled), Q Q^T per head; k-step outermost so that independent products alternate.
+                // enabled); k-step outermost so that the two products alternate.
                 {
-                    const uint32_t r0 = (uint32_t)gp_u * (kSub * 128 >> 4), r1 = r0 + (kSub * 128 >> 4);
+                    const uint32_t r0 = (uint32_t)gp_u * (kSub * 128 >> 4);
                     const uint32_t ma0 = gp_u == 0 ? 0u : 0xffffffffu, ma2 = gp_u == 2 ? 0u : 0xffffffffu;
-                    const uint32_t all = 0xffffffffu;
                     uint32_t ak = lK[st], aq = lQ;
                     if (gp_u == 2) TC4_PSTAMP(i_gp, 6);
 #pragma unroll 1
                     for (int j = 0; j < 8; j++) {
                         umma_lo_unit_e(tm + kColG, ak, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
-                        if (kOutput) {
-                            umma_lo_unit_e(tm + kColP, aq, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
-                            // Q Q^T: only its diagonal (|q_t|^2) is read
-                            umma_lo_unit_e(tm + kColQQ, aq, aq + r0, idesc32, j, ma0, all, ma2, all);
-                            umma_lo_unit_e(tm + kColQQ, aq, aq + r1, idesc32, j, all, ma0, all, ma2);
-                        }
+                        if (kOutput) umma_lo_unit_e(tm + kColP, aq, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
                         const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
                         ak += big;
                         aq += big;
@@ -607,19 +602,30 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
         const cplx at = tk.at, vg = tk.vg;
         const float be = tk.be;
         TC4_STAMP(2);
-        // ---- Gram diagonals: |k_t|^-1, |q_t|^-1
+        // ---- |q_t|^-1 from the Q tile row (swizzled 16-byte pieces): the compute warps have time for it while
+        // they wait for UMMAs, and the tensor pipe is the busier resource
+        float mt = 0.f;
+        if (kOutput) {
+            if (!warp_wait(&sm.full_q, ph, ab)) { code = 11; break; }
+            float qq = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < 2; sl++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint4 r = *reinterpret_cast<const uint4*>(sm.q + sl * kSlab + t * 128 + ((j ^ (t & 7)) << 4));
+                    float f[8];
+                    unpack8(r, f);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) qq = fmaf(f[e], f[e], qq);
+                }
+            mt = rsqrtf(qq + kEps);
+        }
+        // ---- Gram rows of the own head: |k_t|^-1 from the diagonal
         if (!warp_wait(&sm.mma_gp, ph, ab)) { code = 13; break; }
         tc_fence_after();
         TC4_STAMP(3);
         float gs[32], p[32];
-        float mt = 0.f, pd = 0.f;
-        if (kOutput) {
-            tmem_ld32(tlane + kColQQ, p);
-            float qd = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; i++) qd = (i == tl) ? p[i] : qd;
-            mt = rsqrtf(qd + kEps);
-        }
+        float pd = 0.f;
         tmem_ld32(tlane + kColG + 32 * (J & 1), gs);
         float gd = 0.f;
 #pragma unroll
