@@ -36,21 +36,46 @@ namespace tc4 {
 
 constexpr int kC = 128, kD = 128, kSub = 32, kSteps = kC / kSub;
 constexpr int kThreads = 160;
-constexpr uint32_t kTmemCols = 256;
-// G and P: 64 columns each - a pair of heads per UMMA, a thread reads the 32 columns of its own head
-constexpr uint32_t kColG = 0, kColP = 64, kColKappa = 128, kColRho = 160, kColUp = 192;
 constexpr uint32_t kSlab = 128 * 128;          // 64 bf16 columns x 128 rows
 constexpr uint32_t kTile = 2 * kSlab;          // 32 KB
-constexpr uint32_t kSmallSlab = 32 * 128;      // 32-row operand tiles: 4 KB per 64 columns
-constexpr uint32_t kSmallTile = 2 * kSmallSlab;
 
-struct __align__(1024) Smem {
+// Sizes that differ between the two passes.  The local pass carries only z (4 operand rows per head instead
+// of 8, half the tensor-memory columns) and needs no Q tile, so three of its thread blocks fit on an SM.
+template <bool kOutput>
+struct Cfg {
+    static constexpr int kRows = kOutput ? 8 : 4;               // state / omega operand rows per head (hi + lo)
+    static constexpr int kN = 4 * kRows;                        // rows of the two small operand tiles
+    static constexpr uint32_t kSmallSlab = kN * 128;            // bytes per 64 columns
+    static constexpr uint32_t kSmallTile = 2 * kSmallSlab;
+    static constexpr uint32_t kTmemCols = kOutput ? 256 : 128;
+    // G and P: 64 columns each - a pair of heads per UMMA, a thread reads the 32 columns of its own head
+    static constexpr uint32_t kColG = 0, kColP = 64;
+    static constexpr uint32_t kColKappa = kOutput ? 128 : 64, kColRho = 160, kColUp = kOutput ? 192 : 80;
+    static constexpr int kBlocksPerSm = kOutput ? 2 : 3;
+};
+
+template <bool kOutput>
+struct Smem;
+template <>
+struct __align__(1024) Smem<true> {
     uint8_t k[2][kTile];        // rows 32 j + t: token t of head j (TMA, double buffered)
     uint8_t q[kTile];
-    uint8_t s_tile[kSmallTile]; // rows 8 j + {z_re hi, lo, z_im hi, lo, r_re hi, lo, r_im hi, lo}, columns d
-    uint8_t o_tile[kSmallTile]; // rows 8 j + {uz_re hi, lo, uz_im hi, lo, ur_re hi, lo, ur_im hi, lo}, columns = tile rows
+    uint8_t s_tile[Cfg<true>::kSmallTile]; // rows 8 j + {z_re hi, lo, z_im hi, lo, r_re hi, lo, r_im hi, lo}, columns d
+    uint8_t o_tile[Cfg<true>::kSmallTile]; // rows 8 j + {uz_re hi, lo, uz_im hi, lo, ur_re hi, lo, ur_im hi, lo}, columns = tile rows
     __nv_bfloat162 a[kC];       // a_t of tile row r (a is a bf16 pair in the reference's storage)
     float2 bp[2][4];            // product of a over the sub-block, per head, by step parity
+    uint64_t full_k[2], full_q, mma_gp, mma_kr, mma_up, gp_free, s_ready, omega_ready, bp_ready, drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+template <>
+struct __align__(1024) Smem<false> {
+    uint8_t k[2][kTile];
+    uint8_t s_tile[Cfg<false>::kSmallTile]; // rows 4 j + {z_re hi, lo, z_im hi, lo}, columns d
+    uint8_t o_tile[Cfg<false>::kSmallTile]; // rows 4 j + {uz_re hi, lo, uz_im hi, lo}, columns = tile rows
+    uint8_t q[16];              // never used: keeps the code of the two passes the same
+    __nv_bfloat162 a[kC];
+    float2 bp[2][4];
     uint64_t full_k[2], full_q, mma_gp, mma_kr, mma_up, gp_free, s_ready, omega_ready, bp_ready, drain;
     uint32_t tmem_base;
     int abort_flag;
@@ -75,15 +100,15 @@ __device__ __forceinline__ cplx cshfl(cplx v, int src) {
     return {__shfl_sync(0xffffffffu, v.r, src), __shfl_sync(0xffffffffu, v.i, src)};
 }
 __device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-// element (row n, column kk) of a 32-row K-major bf16 operand tile with 128-byte swizzle
-__device__ __forceinline__ uint32_t small_off(int n, int kk) {
-    return (uint32_t)(kk >> 6) * kSmallSlab + (uint32_t)n * 128u + (uint32_t)((((kk & 63) >> 3) ^ (n & 7)) << 4) +
+// element (row n, column kk) of a small K-major bf16 operand tile with 128-byte swizzle (slab: bytes per 64 columns)
+__device__ __forceinline__ uint32_t small_off(uint32_t slab, int n, int kk) {
+    return (uint32_t)(kk >> 6) * slab + (uint32_t)n * 128u + (uint32_t)((((kk & 63) >> 3) ^ (n & 7)) << 4) +
            (uint32_t)(kk & 7) * 2u;
 }
-__device__ __forceinline__ void st_hi_lo(uint8_t* tile, int n, int kk, float x) {
+__device__ __forceinline__ void st_hi_lo(uint8_t* tile, uint32_t slab, int n, int kk, float x) {
     const __nv_bfloat16 hi = __float2bfloat16_rn(x);
-    *reinterpret_cast<__nv_bfloat16*>(tile + small_off(n, kk)) = hi;
-    *reinterpret_cast<__nv_bfloat16*>(tile + small_off(n + 1, kk)) = __float2bfloat16_rn(x - __bfloat162float(hi));
+    *reinterpret_cast<__nv_bfloat16*>(tile + small_off(slab, n, kk)) = hi;
+    *reinterpret_cast<__nv_bfloat16*>(tile + small_off(slab, n + 1, kk)) = __float2bfloat16_rn(x - __bfloat162float(hi));
 }
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* ab) {
     const bool ok = mbar_wait(bar, parity, ab);
@@ -185,12 +210,13 @@ __device__ __forceinline__ bool warp_test(uint64_t* bar, uint32_t parity) {
 // of batch row b.  Every barrier completes once per step, so its parity is that of g.
 // ------------------------------------------------------------------------------------------
 template <bool kOutput>
-__device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const CUtensorMap* tmQ, const Args& a) {
+__device__ __forceinline__ void producer(Smem<kOutput>& sm, const CUtensorMap* tmK, const CUtensorMap* tmQ, const Args& a) {
+    using C = Cfg<kOutput>;
     volatile int* ab = &sm.abort_flag;
     const uint32_t tm = sm.tmem_base;
-    constexpr uint32_t idesc32 = umma_idesc_bf16(128, 32, false, false);
+    constexpr uint32_t idesc_s = umma_idesc_bf16(128, C::kN, false, false);   // kappa / rho: N = state rows
     constexpr uint32_t idesc64 = umma_idesc_bf16(128, 64, false, false);
-    constexpr uint32_t idesc_up = umma_idesc_bf16(128, 32, true, false);
+    constexpr uint32_t idesc_up = umma_idesc_bf16(128, C::kN, true, false);
     const uint32_t kaddr[2] = {smem_u32(sm.k[0]), smem_u32(sm.k[1])};
     const uint32_t qaddr = smem_u32(sm.q), saddr = smem_u32(sm.s_tile), oaddr = smem_u32(sm.o_tile);
     bool pend_k[2] = {false, false}, pend_q = false;
@@ -221,7 +247,7 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
     const uint32_t lK[2] = {desc_lo(kaddr[0], 16), desc_lo(kaddr[1], 16)};
     const uint32_t lKt[2] = {desc_lo(kaddr[0], kSlab), desc_lo(kaddr[1], kSlab)};
     const uint32_t lQ = desc_lo(qaddr, 16), lS = desc_lo(saddr, 16), lO = desc_lo(oaddr, 16);
-    constexpr uint32_t kBigJump = (kSlab >> 4) - 8, kSmallJump = (kSmallSlab >> 4) - 8;
+    constexpr uint32_t kBigJump = (kSlab >> 4) - 8, kSmallJump = (C::kSmallSlab >> 4) - 8;
     int i_gp = 0, gp_u = 0, i_kr = 0, i_up = 0, i_lq = 1, i_lk = 2;
     bool k_ok = false, q_ok = !kOutput;
     uint64_t last = global_ns();
@@ -244,7 +270,7 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
                 uint32_t al = lKt[st], bl = lO;
 #pragma unroll 1
                 for (int j = 0; j < 8; j++) {
-                    umma_lo_e(tm + kColUp, al, bl, idesc_up, j);
+                    umma_lo_e(tm + C::kColUp, al, bl, idesc_up, j);
                     al += 2048 >> 4;
                     bl += (j == 3) ? 2 + kSmallJump : 2;
                 }
@@ -259,8 +285,8 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
                 uint32_t ak = lK[st], aq = lQ, bl = lS;
 #pragma unroll 1
                 for (int j = 0; j < 8; j++) {
-                    umma_lo_e(tm + kColKappa, ak, bl, idesc32, j);
-                    if (kOutput) umma_lo_e(tm + kColRho, aq, bl, idesc32, j);
+                    umma_lo_e(tm + C::kColKappa, ak, bl, idesc_s, j);
+                    if (kOutput) umma_lo_e(tm + C::kColRho, aq, bl, idesc_s, j);
                     const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
                     ak += big;
                     aq += big;
@@ -295,8 +321,8 @@ __device__ __forceinline__ void producer(Smem& sm, const CUtensorMap* tmK, const
                     if (gp_u == 2) TC4_PSTAMP(i_gp, 6);
 #pragma unroll 1
                     for (int j = 0; j < 8; j++) {
-                        umma_lo_unit_e(tm + kColG, ak, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
-                        if (kOutput) umma_lo_unit_e(tm + kColP, aq, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
+                        umma_lo_unit_e(tm + C::kColG, ak, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
+                        if (kOutput) umma_lo_unit_e(tm + C::kColP, aq, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
                         const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
                         ak += big;
                         aq += big;
@@ -369,7 +395,7 @@ struct BlockOut {   // what a sub-block walk hands back
 // u~ = n u, x~ = n x) and C (in-block read-out; the correction is read before its step,
 // exact_correction.cu:90-94).  Reads G / P from tensor memory itself.
 template <bool kOutput>
-__device__ __forceinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane, int J, int tl, cplx at, cplx vg, float be,
+__device__ __forceinline__ BlockOut robust_block(const Smem<kOutput>& sm, uint32_t tlane, int J, int tl, cplx at, cplx vg, float be,
                                              float nt, cplx kz, cplx kr, cplx rz, cplx rr) {
     const float bnn = be * nt * nt;
     cplx W = at, S = at;   // inclusive prefix / suffix products of a over the sub-block
@@ -392,7 +418,7 @@ __device__ __forceinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane,
 #pragma unroll 1
         for (int grp = 3; grp >= 0; grp--) {
             float g8[8];
-            tmem_ld8(tlane + kColG + 32 * (J & 1) + grp * 8, g8);
+            tmem_ld8(tlane + Cfg<kOutput>::kColG + 32 * (J & 1) + grp * 8, g8);
 #pragma unroll
             for (int e = 7; e >= 0; e--) {
                 const int i = grp * 8 + e;
@@ -441,7 +467,7 @@ __device__ __forceinline__ BlockOut robust_block(const Smem& sm, uint32_t tlane,
 #pragma unroll 1
         for (int grp = 3; grp >= 0; grp--) {
             float p8[8];
-            tmem_ld8(tlane + kColP + 32 * (J & 1) + grp * 8, p8);
+            tmem_ld8(tlane + Cfg<kOutput>::kColP + 32 * (J & 1) + grp * 8, p8);
 #pragma unroll
             for (int e = 7; e >= 0; e--) {
                 const int i = grp * 8 + e;
@@ -491,7 +517,8 @@ __device__ __forceinline__ ItemPos item_pos(const Args& a, int item) {
 // prefix product a_16 ... a_t = D_t, and neither half leaves the float range unless one half alone decays by
 // more than 1e-30 (then, or with the zero padding behind the sequence end, the explicit walk is taken).
 // Publishes a_t and the block product W_31 for step g (read by all threads in the state hand-off).
-__device__ __forceinline__ Tok prepare(Smem& sm, const uint4& rec, int g, int J, int tl) {
+template <bool kOutput>
+__device__ __forceinline__ Tok prepare(Smem<kOutput>& sm, const uint4& rec, int g, int J, int tl) {
     Tok k;
     k.at = {bf_lo(rec.x), bf_hi(rec.x)};
     k.vg = {bf_lo(rec.y), bf_hi(rec.y)};
@@ -536,7 +563,9 @@ __device__ __forceinline__ Tok prepare(Smem& sm, const uint4& rec, int g, int J,
 }
 
 template <bool kOutput>
-__device__ __forceinline__ void compute(Smem& sm, const Args& a) {
+__device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
+    using C = Cfg<kOutput>;
+    constexpr int R = C::kRows;
     volatile int* ab = &sm.abort_flag;
     const int t = threadIdx.x, J = t >> 5, tl = t & 31;
     const int H = a.H, L = a.L;
@@ -552,7 +581,7 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
     {
         const bool valid = cur.c * kC + tl < L;
         const uint4 first = valid ? __ldg(a.rec + rec_index(a, cur.b, cur.c, 0, cur.h0 + J, tl)) : zero4;
-        tk = prepare(sm, first, 0, J, tl);
+        tk = prepare<kOutput>(sm, first, 0, J, tl);
     }
     for (int g = 0; g < NS && !code; g++) {
         const uint32_t ph = g & 1;
@@ -580,11 +609,11 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
         TC4_STAMP(11);
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            st_hi_lo(sm.s_tile, 8 * u + 0, t, Sz[u].r);
-            st_hi_lo(sm.s_tile, 8 * u + 2, t, Sz[u].i);
+            st_hi_lo(sm.s_tile, C::kSmallSlab, R * u + 0, t, Sz[u].r);
+            st_hi_lo(sm.s_tile, C::kSmallSlab, R * u + 2, t, Sz[u].i);
             if (kOutput) {
-                st_hi_lo(sm.s_tile, 8 * u + 4, t, Sr[u].r);
-                st_hi_lo(sm.s_tile, 8 * u + 6, t, Sr[u].i);
+                st_hi_lo(sm.s_tile, C::kSmallSlab, R * u + 4, t, Sr[u].r);
+                st_hi_lo(sm.s_tile, C::kSmallSlab, R * u + 6, t, Sr[u].i);
             }
         }
         fence_proxy_async();
@@ -626,7 +655,7 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
         TC4_STAMP(3);
         float gs[32], p[32];
         float pd = 0.f;
-        tmem_ld32(tlane + kColG + 32 * (J & 1), gs);
+        tmem_ld32(tlane + C::kColG + 32 * (J & 1), gs);
         float gd = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; i++) gd = (i == tl) ? gs[i] : gd;
@@ -638,7 +667,7 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
 #pragma unroll
             for (int i = 0; i < 32; i++) gs[i] = (i < tl) ? -bnn * gs[i] : 0.f;
             if (kOutput) {
-                tmem_ld32(tlane + kColP + 32 * (J & 1), p);
+                tmem_ld32(tlane + C::kColP + 32 * (J & 1), p);
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     pd = (i == tl) ? p[i] : pd;
@@ -652,8 +681,8 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
             tc_fence_after();
             TC4_STAMP(4);
             float k8[8], r8[8];
-            if (kOutput) tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
-            else tmem_ld8(tlane + kColKappa + 8 * J, k8);
+            if (kOutput) tmem_ld8x2(tlane + C::kColKappa + 8 * J, k8, tlane + C::kColRho + 8 * J, r8);
+            else tmem_ld4(tlane + C::kColKappa + 4 * J, k8);
             const cplx rkz = cmul(tk.R, cplx{k8[0] + k8[1], k8[2] + k8[3]});
             cplx cw = {nt * be * (tk.viw.r - nt * rkz.r), nt * be * (tk.viw.i - nt * rkz.i)};
             cplx cx = {0.f, 0.f}, accu = {0.f, 0.f}, accx = {0.f, 0.f};
@@ -689,15 +718,15 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
             }
         } else {
             if (kOutput) {
-                tmem_ld32(tlane + kColP + 32 * (J & 1), p);
+                tmem_ld32(tlane + C::kColP + 32 * (J & 1), p);
 #pragma unroll
                 for (int i = 0; i < 32; i++) pd = (i == tl) ? p[i] : pd;
             }
             if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
             tc_fence_after();
-            float k8[8], r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (kOutput) tmem_ld8x2(tlane + kColKappa + 8 * J, k8, tlane + kColRho + 8 * J, r8);
-            else tmem_ld8(tlane + kColKappa + 8 * J, k8);
+            float k8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (kOutput) tmem_ld8x2(tlane + C::kColKappa + 8 * J, k8, tlane + C::kColRho + 8 * J, r8);
+            else tmem_ld4(tlane + C::kColKappa + 4 * J, k8);
             o = robust_block<kOutput>(sm, tlane, J, tl, at, vg, be, nt, cplx{k8[0] + k8[1], k8[2] + k8[3]},
                                       cplx{k8[4] + k8[5], k8[6] + k8[7]}, cplx{r8[0] + r8[1], r8[2] + r8[3]},
                                       cplx{r8[4] + r8[5], r8[6] + r8[7]});
@@ -707,11 +736,11 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
         }
         TC4_STAMP(5);
         // ---- omega columns of the state update: z += sum_t Gamma[31,t] u~_t k_t, r -= sum_t Gamma[31,t] x~_t k_t
-        st_hi_lo(sm.o_tile, 8 * J + 0, t, o.wh.r);
-        st_hi_lo(sm.o_tile, 8 * J + 2, t, o.wh.i);
+        st_hi_lo(sm.o_tile, C::kSmallSlab, R * J + 0, t, o.wh.r);
+        st_hi_lo(sm.o_tile, C::kSmallSlab, R * J + 2, t, o.wh.i);
         if (kOutput) {
-            st_hi_lo(sm.o_tile, 8 * J + 4, t, o.xh.r);
-            st_hi_lo(sm.o_tile, 8 * J + 6, t, o.xh.i);
+            st_hi_lo(sm.o_tile, C::kSmallSlab, R * J + 4, t, o.xh.r);
+            st_hi_lo(sm.o_tile, C::kSmallSlab, R * J + 6, t, o.xh.i);
         }
         fence_proxy_async();
         __syncwarp();
@@ -733,7 +762,7 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
         // for first: prepare() arrives on the same barrier for the next step, and a wait must never be two
         // phases behind its barrier.
         if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 14; break; }
-        if (g + 1 < NS) tk = prepare(sm, rec, g + 1, J, tl);
+        if (g + 1 < NS) tk = prepare<kOutput>(sm, rec, g + 1, J, tl);
         TC4_STAMP(8);
         // ---- state hand-off: S <- BP S + K^T omega, column d = t of every head
         if (!warp_wait(&sm.mma_up, ph, ab)) { code = 15; break; }
@@ -741,15 +770,16 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
         TC4_STAMP(6);
         if (!kOutput || step + 1 < kSteps) {
             float up[32];
-            tmem_ld32(tlane + kColUp, up);
+            if (kOutput) tmem_ld32(tlane + C::kColUp, up);
+            else tmem_ld16(tlane + C::kColUp, up);
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const cplx bpu = {sm.bp[ph][u].x, sm.bp[ph][u].y};
                 const cplx nz = cmul(bpu, Sz[u]);
-                Sz[u] = {nz.r + up[8 * u] + up[8 * u + 1], nz.i + up[8 * u + 2] + up[8 * u + 3]};
+                Sz[u] = {nz.r + up[R * u] + up[R * u + 1], nz.i + up[R * u + 2] + up[R * u + 3]};
                 if (kOutput) {
                     const cplx nr = cmul(bpu, Sr[u]);
-                    Sr[u] = {nr.r + up[8 * u + 4] + up[8 * u + 5], nr.i + up[8 * u + 6] + up[8 * u + 7]};
+                    Sr[u] = {nr.r + up[R * u + 4] + up[R * u + 5], nr.i + up[R * u + 6] + up[R * u + 7]};
                 } else {
                     gam[u] = cmul(bpu, gam[u]);
                 }
@@ -779,10 +809,10 @@ __device__ __forceinline__ void compute(Smem& sm, const Args& a) {
 }
 
 template <bool kOutput>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, Cfg<kOutput>::kBlocksPerSm)
 scan_tc4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ, const Args a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+    Smem<kOutput>& sm = *reinterpret_cast<Smem<kOutput>*>(smem_raw);
     const int warp = threadIdx.x >> 5;
     if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicCAS(a.status, 0, 399);
@@ -798,9 +828,9 @@ scan_tc4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         fence_barrier_init();
     }
     // rows of the two small operand tiles that a pass does not write stay zero for the whole kernel
-    for (int i = threadIdx.x; i < 2 * (int)kSmallTile / 16; i += kThreads)
+    for (int i = threadIdx.x; i < 2 * (int)Cfg<kOutput>::kSmallTile / 16; i += kThreads)
         reinterpret_cast<uint4*>(sm.s_tile)[i] = make_uint4(0, 0, 0, 0);   // s_tile and o_tile are adjacent
-    if (warp == 4) tmem_alloc(&sm.tmem_base, kTmemCols);
+    if (warp == 4) tmem_alloc(&sm.tmem_base, Cfg<kOutput>::kTmemCols);
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -820,7 +850,7 @@ scan_tc4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     __syncthreads();
     if (warp == 4) {
         __syncwarp();
-        tmem_dealloc(sm.tmem_base, kTmemCols);
+        tmem_dealloc(sm.tmem_base, Cfg<kOutput>::kTmemCols);
     }
 }
 
@@ -936,13 +966,15 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
     using namespace tc4;
     CUtensorMap tmK, tmQ;
     if (!make_tile_map(&tmK, k, B, L, H) || !make_tile_map(&tmQ, output ? q : k, B, L, H)) return CDSSM_ERR_CUDA;
-    const size_t smem = sizeof(Smem);
+    const size_t smem = output ? sizeof(Smem<true>) : sizeof(Smem<false>);
     static bool attr = false;
     static int sms = 0;
     if (!attr) {
-        if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     (int)sizeof(Smem<true>))))
             return rc;
-        if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     (int)sizeof(Smem<false>))))
             return rc;
         int dev = 0;
         if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
@@ -965,7 +997,8 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
     const long long items = (long long)B * a.NC * a.HG;
     if (items > 0x7fffffff / 8) return CDSSM_ERR_UNSUPPORTED;
     a.items = (int)items;
-    const int grid = (int)(items < 2LL * sms ? items : 2LL * sms);
+    const long long resident = (long long)(output ? Cfg<true>::kBlocksPerSm : Cfg<false>::kBlocksPerSm) * sms;
+    const int grid = (int)(items < resident ? items : resident);
     if (output) scan_tc4_kernel<true><<<grid, kThreads, smem, st>>>(tmK, tmQ, a);
     else scan_tc4_kernel<false><<<grid, kThreads, smem, st>>>(tmK, tmQ, a);
     return check_launch();
