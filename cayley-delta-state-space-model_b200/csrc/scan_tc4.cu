@@ -64,7 +64,7 @@ struct __align__(1024) Smem<true> {
     uint8_t o_tile[Cfg<true>::kSmallTile]; // rows 8 j + {uz_re hi, lo, uz_im hi, lo, ur_re hi, lo, ur_im hi, lo}, columns = tile rows
     __nv_bfloat162 a[kC];       // a_t of tile row r (a is a bf16 pair in the reference's storage)
     float2 bp[2][4];            // product of a over the sub-block, per head, by step parity
-    uint64_t full_k[2], full_q, mma_gp, mma_kr, mma_up, gp_free, s_ready, omega_ready, bp_ready, drain;
+    uint64_t full_k[2], full_q, mma_g, mma_p, mma_kr, mma_up, g_free, p_free, s_ready, omega_ready, bp_ready, drain;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -76,7 +76,7 @@ struct __align__(1024) Smem<false> {
     uint8_t q[16];              // never used: keeps the code of the two passes the same
     __nv_bfloat162 a[kC];
     float2 bp[2][4];
-    uint64_t full_k[2], full_q, mma_gp, mma_kr, mma_up, gp_free, s_ready, omega_ready, bp_ready, drain;
+    uint64_t full_k[2], full_q, mma_g, mma_p, mma_kr, mma_up, g_free, p_free, s_ready, omega_ready, bp_ready, drain;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -248,15 +248,16 @@ __device__ __forceinline__ void producer(Smem<kOutput>& sm, const CUtensorMap* t
     const uint32_t lKt[2] = {desc_lo(kaddr[0], kSlab), desc_lo(kaddr[1], kSlab)};
     const uint32_t lQ = desc_lo(qaddr, 16), lS = desc_lo(saddr, 16), lO = desc_lo(oaddr, 16);
     constexpr uint32_t kBigJump = (kSlab >> 4) - 8, kSmallJump = (C::kSmallSlab >> 4) - 8;
-    int i_gp = 0, gp_u = 0, i_kr = 0, i_up = 0, i_lq = 1, i_lk = 2;
-    bool k_ok = false, q_ok = !kOutput;
+    // Progress counters: UMMA groups issued (G, P, kappa / rho, state update) and tiles requested.
+    int i_g = 0, i_p = 0, i_kr = 0, i_up = 0, i_lq = 1, i_lk = 2;
+    bool k_ok = false, q_ok = false;   // the K tile of step i_g / the Q tile of step i_p has landed
     uint64_t last = global_ns();
     uint32_t idle = 0;
 #define TC4_PSTAMP(n, idx) do { if (a.trace && (threadIdx.x & 31) == 0 && blockIdx.x == a.trace_block && (n) >= a.trace_g0 && (n) < a.trace_g0 + 16) a.trace[(((n) - a.trace_g0) * 5 + 4) * 16 + (idx)] = clock64(); } while (0)
     auto par = [](int n) { return (uint32_t)(n & 1); };
-    // Tasks in order of urgency: the state update and kappa / rho sit on the compute warps' critical path,
-    // the tile loads and the Gram blocks of the NEXT step do not; the Gram blocks are issued one head at a
-    // time so that an urgent task never waits behind more than sixteen UMMAs.
+    // Tasks in order of urgency: the state update and kappa / rho sit on the compute warps' critical path; the
+    // tile loads and the Gram blocks of the NEXT step do not.  G (needs only the K tile) and P (needs the Q
+    // tile, whose single buffer is refilled late) are separate tasks so that G is never held back by Q.
     while (i_up < NS) {
         bool progress = false;
         // state update: A = K tile read MN-major (M = d, two 64-wide groups 16 KB apart; K = tile rows,
@@ -278,7 +279,8 @@ __device__ __forceinline__ void producer(Smem<kOutput>& sm, const CUtensorMap* t
             umma_commit_e(&sm.mma_up);
             TC4_PSTAMP(i_up, 3);
             i_up++; progress = true;
-        } else if (i_kr < i_gp && warp_test(&sm.s_ready, par(i_kr))) {   // kappa = K S^T, rho = Q S^T
+        } else if (i_kr < i_g && (!kOutput || i_kr < i_p) && warp_test(&sm.s_ready, par(i_kr))) {
+            // kappa = K S^T, rho = Q S^T (G and P of the step have been issued, so its tiles have landed)
             const int st = i_kr & 1;
             tc_fence_after();
             {
@@ -301,41 +303,49 @@ __device__ __forceinline__ void producer(Smem<kOutput>& sm, const CUtensorMap* t
             if (i_lk < NS) { TC4_PSTAMP(i_lk, 5); load_tile(sm.k[i_lk & 1], tmK, &sm.full_k[i_lk & 1], i_lk); pend_k[i_lk & 1] = true; }
             i_lk++; progress = true;
         } else if (kOutput && i_lq <= i_kr && i_lq <= NS && warp_test(&sm.mma_kr, par(i_lq - 1)) &&
-                   warp_test(&sm.gp_free, par(i_lq - 1))) {
-            // Q tile of step n is free once its UMMAs have completed (mma_kr is committed after mma_gp of the
-            // same step, so it covers both) and the compute warps have taken |q| from it (before gp_free)
+                   warp_test(&sm.p_free, par(i_lq - 1))) {
+            // Q tile of step n is free once its UMMAs have completed (rho is committed after P of the same step,
+            // so mma_kr covers both) and the compute warps have taken |q| from it (before p_free)
             if (i_lq < NS) { TC4_PSTAMP(i_lq, 4); load_tile(sm.q, tmQ, &sm.full_q, i_lq); pend_q = true; }
             i_lq++; progress = true;
-        } else if (i_gp < NS) {   // diagonal Gram blocks of step i_gp, head gp_u
-            const int n = i_gp, st = n & 1;
-            if (!k_ok && warp_test(&sm.full_k[st], (n >> 1) & 1)) { k_ok = true; pend_k[st] = false; }
-            if (!q_ok && warp_test(&sm.full_q, par(n))) { q_ok = true; pend_q = false; }
-            if (k_ok && q_ok && (n == 0 || gp_u > 0 || warp_test(&sm.gp_free, par(n - 1)))) {
-                if (gp_u == 0) { tc_fence_after(); TC4_PSTAMP(i_gp, 0); }
-                // One pair of heads per visit: G and P of the pair as one N = 64 UMMA each (the pair's 64 lanes
-                // enabled); k-step outermost so that the two products alternate.
-                {
-                    const uint32_t r0 = (uint32_t)gp_u * (kSub * 128 >> 4);
-                    const uint32_t ma0 = gp_u == 0 ? 0u : 0xffffffffu, ma2 = gp_u == 2 ? 0u : 0xffffffffu;
+        } else {
+            if (kOutput && i_p < NS && i_p < i_g) {   // P = Q K^T of step i_p, the diagonal blocks of both pairs of heads
+                if (!q_ok && warp_test(&sm.full_q, par(i_p))) { q_ok = true; pend_q = false; }
+                if (q_ok && (i_p == 0 || warp_test(&sm.p_free, par(i_p - 1)))) {
+                    const int st = i_p & 1;
+                    tc_fence_after();
                     uint32_t ak = lK[st], aq = lQ;
-                    if (gp_u == 2) TC4_PSTAMP(i_gp, 6);
+                    constexpr uint32_t r2 = 2 * (kSub * 128 >> 4), all = 0xffffffffu;
 #pragma unroll 1
                     for (int j = 0; j < 8; j++) {
-                        umma_lo_unit_e(tm + C::kColG, ak, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
-                        if (kOutput) umma_lo_unit_e(tm + C::kColP, aq, ak + r0, idesc64, j, ma0, ma0, ma2, ma2);
+                        umma_lo_unit_e(tm + C::kColP, aq, ak, idesc64, j, 0u, 0u, all, all);
+                        umma_lo_unit_e(tm + C::kColP, aq, ak + r2, idesc64, j, all, all, 0u, 0u);
                         const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
                         ak += big;
                         aq += big;
                     }
-                    if (gp_u == 2) TC4_PSTAMP(i_gp, 7);
+                    umma_commit_e(&sm.mma_p);
+                    TC4_PSTAMP(i_p, 1);
+                    i_p++; q_ok = false; progress = true;
                 }
-                gp_u++;
-                if (++gp_u == 4) {
-                    umma_commit_e(&sm.mma_gp);
-                    TC4_PSTAMP(i_gp, 1);
-                    gp_u = 0; i_gp++; k_ok = false; q_ok = !kOutput;
+            }
+            if (!progress && i_g < NS) {   // G = K K^T of step i_g, likewise
+                const int st = i_g & 1;
+                if (!k_ok && warp_test(&sm.full_k[st], (i_g >> 1) & 1)) { k_ok = true; pend_k[st] = false; }
+                if (k_ok && (i_g == 0 || warp_test(&sm.g_free, par(i_g - 1)))) {
+                    tc_fence_after();
+                    TC4_PSTAMP(i_g, 0);
+                    uint32_t ak = lK[st];
+                    constexpr uint32_t r2 = 2 * (kSub * 128 >> 4), all = 0xffffffffu;
+#pragma unroll 1
+                    for (int j = 0; j < 8; j++) {
+                        umma_lo_unit_e(tm + C::kColG, ak, ak, idesc64, j, 0u, 0u, all, all);
+                        umma_lo_unit_e(tm + C::kColG, ak, ak + r2, idesc64, j, all, all, 0u, 0u);
+                        ak += (j == 3) ? 2 + kBigJump : 2;
+                    }
+                    umma_commit_e(&sm.mma_g);
+                    i_g++; k_ok = false; progress = true;
                 }
-                progress = true;
             }
         }
         if (progress) {
@@ -343,7 +353,7 @@ __device__ __forceinline__ void producer(Smem<kOutput>& sm, const CUtensorMap* t
         } else if ((++idle & 7) != 0) {
             __nanosleep(200);
         } else if (__any_sync(0xffffffffu, *ab || global_ns() - last > kWaitLimitNs)) {
-            code = 1 + (i_gp > i_kr) + 2 * (i_kr > i_up);
+            code = 1 + (i_g > i_kr) + 2 * (i_kr > i_up);
             *ab = 1;
             break;
         }
@@ -650,7 +660,7 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
             mt = rsqrtf(qq + kEps);
         }
         // ---- Gram rows of the own head: |k_t|^-1 from the diagonal
-        if (!warp_wait(&sm.mma_gp, ph, ab)) { code = 13; break; }
+        if (!warp_wait(&sm.mma_g, ph, ab)) { code = 13; break; }
         tc_fence_after();
         TC4_STAMP(3);
         float gs[32], p[32];
@@ -663,10 +673,15 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
         const float bnn = be * nt * nt;
         BlockOut o;
         if (tk.fast) {
+            tc_fence_before();
+            __syncwarp();
+            if (tl == 0) mbar_arrive(&sm.g_free);   // G is in registers
             // coefficients of the real system, zero on and above the diagonal
 #pragma unroll
             for (int i = 0; i < 32; i++) gs[i] = (i < tl) ? -bnn * gs[i] : 0.f;
             if (kOutput) {
+                if (!warp_wait(&sm.mma_p, ph, ab)) { code = 16; break; }
+                tc_fence_after();
                 tmem_ld32(tlane + C::kColP + 32 * (J & 1), p);
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
@@ -674,9 +689,11 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
                     p[i] = (i < tl) ? p[i] : 0.f;
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (tl == 0) mbar_arrive(&sm.gp_free);   // every read of this step's Gram blocks is done
+            if (kOutput) {
+                tc_fence_before();
+                __syncwarp();
+                if (tl == 0) mbar_arrive(&sm.p_free);   // P is in registers, |q| has been taken from the Q tile
+            }
             if (!warp_wait(&sm.mma_kr, ph, ab)) { code = 12; break; }
             tc_fence_after();
             TC4_STAMP(4);
@@ -727,12 +744,13 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
             float k8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, r8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (kOutput) tmem_ld8x2(tlane + C::kColKappa + 8 * J, k8, tlane + C::kColRho + 8 * J, r8);
             else tmem_ld4(tlane + C::kColKappa + 4 * J, k8);
+            if (kOutput) { if (!warp_wait(&sm.mma_p, ph, ab)) { code = 16; break; } tc_fence_after(); }
             o = robust_block<kOutput>(sm, tlane, J, tl, at, vg, be, nt, cplx{k8[0] + k8[1], k8[2] + k8[3]},
                                       cplx{k8[4] + k8[5], k8[6] + k8[7]}, cplx{r8[0] + r8[1], r8[2] + r8[3]},
                                       cplx{r8[4] + r8[5], r8[6] + r8[7]});
             tc_fence_before();
             __syncwarp();
-            if (tl == 0) mbar_arrive(&sm.gp_free);
+            if (tl == 0) { mbar_arrive(&sm.g_free); if (kOutput) mbar_arrive(&sm.p_free); }
         }
         TC4_STAMP(5);
         // ---- omega columns of the state update: z += sum_t Gamma[31,t] u~_t k_t, r -= sum_t Gamma[31,t] x~_t k_t
@@ -820,8 +838,8 @@ scan_tc4_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     }
     if (threadIdx.x == 0) {
         mbar_init(&sm.full_k[0], 1); mbar_init(&sm.full_k[1], 1); mbar_init(&sm.full_q, 1);
-        mbar_init(&sm.mma_gp, 1); mbar_init(&sm.mma_kr, 1); mbar_init(&sm.mma_up, 1);
-        mbar_init(&sm.gp_free, 4); mbar_init(&sm.s_ready, 4); mbar_init(&sm.omega_ready, 4);
+        mbar_init(&sm.mma_g, 1); mbar_init(&sm.mma_p, 1); mbar_init(&sm.mma_kr, 1); mbar_init(&sm.mma_up, 1);
+        mbar_init(&sm.g_free, 4); mbar_init(&sm.p_free, 4); mbar_init(&sm.s_ready, 4); mbar_init(&sm.omega_ready, 4);
         mbar_init(&sm.bp_ready, 4);
         mbar_init(&sm.drain, 1);
         sm.abort_flag = 0;
