@@ -92,7 +92,7 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
 
 /* Flags of cdssm_b200_scan_fused_fwd. */
 #define CDSSM_SCAN_DEFAULT 0
-#define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels (the default) */
+#define CDSSM_SCAN_FORCE_SIMT 1    /* use the CUDA-core kernels even where the tensor-core passes apply */
 #define CDSSM_SCAN_REUSE_LOCAL 8    /* the workspace still holds the local pass of exactly these inputs, left
                                       by cdssm_b200_scan_summary_fwd on the same workspace: skip that pass */
 #define CDSSM_SCAN_EXACT 32         /* NOT the reference's chunk semantics: the plain token-by-token recurrence
@@ -101,9 +101,10 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
                                       the recurrent state.  One sequential walk per (batch, head, pair). */
 #define CDSSM_SCAN_TENSOR_CORE 2   /* use the single-pass tcgen05/TMA kernel: bf16, N = 2, D = C = 128,
                                       no tail_state; CDSSM_ERR_UNSUPPORTED for other sizes */
-#define CDSSM_SCAN_TENSOR_CORE4 64 /* local and output pass as tcgen05/TMA kernels that walk four heads' chunks
-                                      per thread block in 32-token sub-blocks: bf16, N = 2, D = C = 128,
-                                      H a multiple of 4, no tail_state; CDSSM_ERR_UNSUPPORTED otherwise */
+#define CDSSM_SCAN_TENSOR_CORE4 64 /* insist on the tcgen05/TMA passes that walk four heads' chunks per thread block
+                                      in 32-token sub-blocks (local and output pass; the default whenever bf16,
+                                      N = 2, D = C = 128, H a multiple of 4 and no tail_state):
+                                      CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
 
 /* Bytes of workspace cdssm_b200_scan_fused_fwd needs for these sizes (0 on bad sizes). */
 CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C);
@@ -113,7 +114,8 @@ CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int 
  * chunk semantics (local scan from zero per chunk of C tokens, decay-only carry between chunks,
  * correction taken before each step) -> shortcut -> read-out with q -> sel_C gate.
  * Supported: even N <= 32, D <= 128, C <= 256, bf16 or fp32 (CUDA-core kernels, three launches);
- * with CDSSM_SCAN_TENSOR_CORE: bf16, N = 2, D = C = 128 in one single-pass tcgen05/TMA kernel.
+ * bf16 with N = 2, D = C = 128, H a multiple of 4 and no tail_state runs on the tensor cores (tcgen05/TMA
+ * local and output pass, four launches); with CDSSM_SCAN_TENSOR_CORE: the older single-pass tcgen05/TMA kernel.
  *   q,k (B,L,H,D) un-normalised; v (B,L,H,N) before the vp scale; gate_raw (B,L,(N+5)*H);
  *   h0 (B,H,N,D) float32 or NULL: carry into the first chunk;
  *   y (B,L,H,N); final_state (B,H,N,D) float32 or NULL: carry after the last chunk;
