@@ -829,7 +829,7 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     // 512 keep the CUDA-core local / output pass: used by the tests to check each tensor-core pass alone.)
     const bool tc4_ok = tail_state == nullptr && scan_tc4_supported(D, N, C, H, dtype);
     const bool tc4_asked = (flags & CDSSM_SCAN_TENSOR_CORE4) != 0;
-    if (!(flags & CDSSM_SCAN_FORCE_SIMT) && !summary_only && (tc4_asked || tc4_ok)) {
+    if (!(flags & CDSSM_SCAN_FORCE_SIMT) && (tc4_asked || tc4_ok)) {
         if (!tc4_ok) return CDSSM_ERR_UNSUPPORTED;
         cudaStream_t st = (cudaStream_t)stream;
         const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
@@ -843,8 +843,8 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
             a.run_local = 0;
         }
         a.run_output = tc_output ? 0 : 1;
-        if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;
-        if (!tc_output) return CDSSM_OK;
+        if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;   // carry pass (+ whatever was kept)
+        if (!tc_output || summary_only) return CDSSM_OK;
         return scan_tc4_pass(true, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L, H, st);
     }
     return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
@@ -918,7 +918,7 @@ extern "C" int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const v
     return scan_fused_impl(nullptr, k, v, gate_raw, log_dt_scale, rope_freqs, h0, nullptr, carry_out,
                            nullptr, total_decay, true, workspace, workspace_bytes, gating_c, omega_thresh,
                            adt_delta, adt_smoothness, adt_eps, 0.f, B, L, H, D, N, C, pos0, segs, dtype,
-                           CDSSM_SCAN_FORCE_SIMT, stream);
+                           CDSSM_SCAN_DEFAULT, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
