@@ -480,7 +480,7 @@ def main():
                 "achieved": abytes / (out_ms / 1e3) / 1e9, "frac": abytes / (out_ms / 1e3) / 1e9 / peak,
                 "how": "a call that reuses the local pass in the workspace (records pre-pass + carry pass + output "
                        "pass), CUDA-event timed; algorithmic bytes of the whole step"}
-            line["roofline"]["traffic"] = 1.63 * abytes
+            line["roofline"]["traffic"] = 1.60 * abytes
             line["roofline"]["traffic_how"] = ("dram bytes read+written per step from an ncu capture of cfg2_L4096 "
                                                "(profiles/scan_tc4_cfg2_L4096.md), scaled by tokens")
         if "summary_ms" in extra:
