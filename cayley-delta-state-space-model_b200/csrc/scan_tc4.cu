@@ -1,30 +1,33 @@
-// Tensor-core output pass with four independent chains per CTA (tcgen05 + TMEM + TMA).
+// Fused scan on the tensor cores with four independent chains per thread block (tcgen05 + TMEM + TMA):
+// a local pass and an output pass around the CUDA-core carry pass, fed by a dynamics pre-pass.
 // Shapes: bf16 storage, state_dim N = 2, head_dim D = 128, chunk C = 128, H a multiple of 4.
 //
-// The single-chain kernel in scan_tc.cu keeps one warp at a time on the critical path.  Here a CTA
+// The single-chain kernel in scan_tc.cu keeps one warp at a time on the critical path.  Here a block
 // owns the same chunk of FOUR heads; the chunk is walked in 32-token sub-blocks and every compute
 // warp owns one head: UMMA tile row 32 j + t is token t of head j's sub-block.  Per sub-block:
-//   G_j = K_j K_j^T, P_j = Q_j K_j^T     : the 32 x 32 diagonal blocks only - one UMMA per head with
-//                                          N = 32 and every output lane but the head's own masked
-//                                          off (disable_output_lane), so all four heads share 32 + 32
-//                                          TMEM columns;
+//   G_j = K_j K_j^T, P_j = Q_j K_j^T     : the 32 x 32 diagonal blocks only - one UMMA (N = 64) per pair
+//                                          of heads with every output lane but the pair's 64 masked off
+//                                          (disable_output_lane), so the four heads share 64 + 64 TMEM
+//                                          columns;
 //   kappa, rho = K S^T, Q S^T            : products with the running states (local state z and
 //                                          correction r of each head, bf16 hi + lo rows) - they
 //                                          replace all off-diagonal work of the chunk form;
 //   solve / read-out                     : each warp solves its own unit-lower-triangular 32 x 32
 //                                          systems (local + correction) by substitution through warp
 //                                          shuffles and reads y out, with rows from tcgen05.ld;
-//   S <- gamma S + K^T Omega             : state update as one UMMA (K tile as MN-major operand),
+//   S <- W_31 S + K^T Omega              : state update as one UMMA (K tile as MN-major operand),
 //                                          thread d applies it to column d of all four heads' states.
-// The four warps never wait for one another except at the UMMA hand-offs, so four chains per CTA and
-// two CTAs per SM are in flight.  Reference semantics: z starts at zero at the chunk start, r starts
-// from the chunk's carry (bf16, from the carry pass), the correction is read before its step.
+// The four warps never wait for one another except at the UMMA hand-offs, so four chains per block and
+// two (output pass) or three (local pass) blocks per SM are in flight.  Reference semantics: z starts at
+// zero at the chunk start, r starts from the chunk's carry (bf16, from the carry pass), the correction is
+// read before its step.
 // Algebra per sub-block with incoming states z0, r0 (restating intra_chunk_scan.cu:100-195 and
 // exact_correction.cu:89-150):
 //   u  = T beta (v - W kappa_z),  x = T beta W kappa_r,  T = (I + M)^-1,  M[t,i] = beta_t Gamma[t,i] G[t,i]
 //   y_t = W_t rho_z,t + sum_{i<=t} Gamma[t,i] P[t,i] u_i + W0_t rho_r,t - sum_{i<t} Gamma0[t,i] P[t,i] x_i
-//   z_end = W_31 z0 + sum_i V_i u_i k_i,   r_end = W_31 r0 - sum_i V_i x_i k_i
-// (W, W0: inclusive / exclusive prefix products of a inside the sub-block, V: exclusive suffix.)
+//   z_end = W_31 z0 + sum_i Gamma[31,i] u_i k_i,   r_end = W_31 r0 - sum_i Gamma[31,i] x_i k_i
+// (W, W0: inclusive / exclusive prefix products of a inside the sub-block.)  The comment above compute()
+// says how the decay products are scaled out of the triangular system.
 #include "cdssm_common.cuh"
 #include "sm100_ptx.cuh"
 #include <cstdlib>
@@ -115,44 +118,10 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
     return __all_sync(0xffffffffu, ok);
 }
 
-// D[tmem] (+)= A * B with every output lane outside [32*unit, 32*unit + 32) disabled
-__device__ __forceinline__ void umma_bf16_unit(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                               bool accumulate, int unit) {
-    const uint32_t m0 = unit == 0 ? 0u : 0xffffffffu, m1 = unit == 1 ? 0u : 0xffffffffu;
-    const uint32_t m2 = unit == 2 ? 0u : 0xffffffffu, m3 = unit == 3 ? 0u : 0xffffffffu;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(m0), "r"(m1), "r"(m2),
-          "r"(m3)
-        : "memory");
-}
 
 
 // The producer warp runs its event loop with all 32 lanes (warp-uniform values keep the descriptors in
 // uniform registers); only one elected lane issues each asynchronous instruction.
-__device__ __forceinline__ void umma_bf16_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            bool accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, e;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "elect.sync _|e, 0xffffffff;\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_bf16_unit_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 bool accumulate, uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
-    asm volatile(
-        "{\n\t.reg .pred p, e;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "elect.sync _|e, 0xffffffff;\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(m0), "r"(m1), "r"(m2),
-          "r"(m3)
-        : "memory");
-}
 // Every shared-memory descriptor used here has the same upper word (stride between eight-row groups
 // 1024 bytes, Blackwell descriptor version, 128-byte swizzle), so only the lower word (start address and
 // leading-dimension offset, both in 16-byte units) is carried around and advanced.
@@ -1005,7 +974,7 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
     a.y = static_cast<__nv_bfloat16*>(y);
     a.status = status; a.trace = g_trace;
     a.trace_g0 = 0; a.trace_block = 0;
-    if (g_trace) {
+    if (g_trace) {   // performance debugging only: which 16 steps of which block are stamped
         if (const char* e = getenv("CDSSM_TC4_TRACE_G0")) a.trace_g0 = atoi(e);
         if (const char* e = getenv("CDSSM_TC4_TRACE_BLOCK")) a.trace_block = atoi(e);
     }
