@@ -39,6 +39,21 @@ def test_tc4_matches_oracle_and_simt(ops, orc, B, H, L, extra):
     assert np.abs(to_np(fin) - to_np(fs)).max() <= 2e-2 * scale
 
 
+@pytest.mark.parametrize("B,H,L", [(2, 4, 32), (1, 8, 33), (1, 4, 127), (3, 4, 128 * 5 + 17), (1, 64, 384), (5, 4, 97)])
+def test_tc4_ragged_lengths_default_path(ops, orc, B, H, L):
+    """Lengths around the sub-block and chunk sizes, more head groups than one block walks at a time; no
+    flags: these shapes take the tensor-core passes by themselves."""
+    inp = _inputs(orc, B, H, L, seed=7 * L + H)
+    y, fin = run_fused(ops, inp, torch.bfloat16, N, C)
+    assert ops.scan_fused_status() == 0
+    ys, fs = run_fused(ops, inp, torch.bfloat16, N, C, flags=ops.FORCE_SIMT)
+    wy13, wf13 = oracle_scan(orc, inp, N, C, orc.ROUND_FP32_STATE)
+    assert rel_err(to_np(y), wy13) <= BF16_TOL / 2
+    assert rel_err(to_np(y), to_np(ys)) <= BF16_TOL / 2
+    scale = max(np.abs(wf13).max(), 1e-3)
+    assert np.abs(to_np(fin) - wf13).max() <= 2e-2 * scale
+
+
 def test_tc4_h0_shortcut_composition(ops, orc):
     B, H, L = 2, 4, 512
     inp = _inputs(orc, B, H, L, seed=77, scale=False)
