@@ -647,11 +647,15 @@ int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_
     CUtensorMap tmK, tmQ;
     if (!make_tile_map(&tmK, k, B, L, H) || !make_tile_map(&tmQ, q, B, L, H)) return CDSSM_ERR_CUDA;
     const size_t smem = sizeof(TcSmem) + 1024;
-    static bool attr = false;
-    if (!attr) {
+    constexpr int kMaxDevices = 64;
+    static bool attr_of_device[kMaxDevices] = {false};   // the shared-memory opt-in is per device
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return CDSSM_ERR_UNSUPPORTED;
+    if (!attr_of_device[dev]) {
         if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
             return rc;
-        attr = true;
+        attr_of_device[dev] = true;
     }
     if (int rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(int), st))) return rc;
     TcArgs a;

@@ -954,20 +954,24 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
     CUtensorMap tmK, tmQ;
     if (!make_tile_map(&tmK, k, B, L, H) || !make_tile_map(&tmQ, output ? q : k, B, L, H)) return CDSSM_ERR_CUDA;
     const size_t smem = output ? sizeof(Smem<true>) : sizeof(Smem<false>);
-    static bool attr = false;
-    static int sms = 0;
-    if (!attr) {
+    // the opt-in to more than 48 KB of dynamic shared memory and the SM count are per device
+    constexpr int kMaxDevices = 64;
+    static int sms_of_device[kMaxDevices] = {0};
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return CDSSM_ERR_UNSUPPORTED;
+    if (sms_of_device[dev] == 0) {
         if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                      (int)sizeof(Smem<true>))))
             return rc;
         if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                      (int)sizeof(Smem<false>))))
             return rc;
-        int dev = 0;
-        if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
-        if (int rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev))) return rc;
-        attr = true;
+        int n = 0;
+        if (int rc = check_cuda(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev))) return rc;
+        sms_of_device[dev] = n;
     }
+    const int sms = sms_of_device[dev];
     Args a;
     a.rec = static_cast<const uint4*>(rec);
     a.ws_gamma = ws_gamma; a.ws_state = ws_state;
