@@ -737,8 +737,8 @@ bool scan_tc4_supported(int D, int N, int C, int H, int dtype);
 size_t scan_tc4_record_bytes(int B, int L, int H);
 int scan_tc4_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
                       void* rec, const DynConsts& dc, int B, int L, int H, int pos0, int segs, cudaStream_t st);
-int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, float* ws_gamma, float* ws_state,
-                  void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st);
+int scan_tc4_pass(bool output, bool two_blocks, const void* q, const void* k, const void* rec, float* ws_gamma,
+                  float* ws_state, void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st);
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -837,15 +837,16 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
         if (int rc = scan_tc4_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, pos0, segs, st))
             return rc;
         if (a.run_local && tc_local) {
-            if (int rc = scan_tc4_pass(false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale, B, L,
-                                       H, st))
+            if (int rc = scan_tc4_pass(false, false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale,
+                                       B, L, H, st))
                 return rc;
             a.run_local = 0;
         }
         a.run_output = tc_output ? 0 : 1;
         if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;   // carry pass (+ whatever was kept)
         if (!tc_output || summary_only) return CDSSM_OK;
-        return scan_tc4_pass(true, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L, H, st);
+        return scan_tc4_pass(true, (flags & 1024) != 0, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L,
+                             H, st);   // bit 1024: the output pass with three tile buffers, two blocks per SM
     }
     return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
 }

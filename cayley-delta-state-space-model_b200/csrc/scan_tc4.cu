@@ -367,6 +367,10 @@ __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 
 struct BlockOut {   // what a sub-block walk hands back
     cplx wh, xh;    // omega columns: Gamma[31,t] u~_t and -Gamma[31,t] x~_t
     cplx ysum;      // pd u~_t + in-block read-out + W rho_z + W0 rho_r (before the |q|^-1 factor)
+    // used by the three-blocks-per-SM variant only:
+    float pd;       // P_raw[t,t]
+    bool ok;        // false: a bounded wait ran out
+    cplx W, W0;     // inclusive / exclusive prefix product of a at this token
 };
 
 // The walk with explicit decay products (any a, including zeros): phases A (coefficients
@@ -496,8 +500,8 @@ __device__ __forceinline__ ItemPos item_pos(const Args& a, int item) {
 // prefix product a_16 ... a_t = D_t, and neither half leaves the float range unless one half alone decays by
 // more than 1e-30 (then, or with the zero padding behind the sequence end, the explicit walk is taken).
 // Publishes a_t and the block product W_31 for step g (read by all threads in the state hand-off).
-template <bool kOutput>
-__device__ __forceinline__ Tok prepare(Smem<kOutput>& sm, const uint4& rec, int g, int J, int tl) {
+template <class SmemT>
+__device__ __forceinline__ Tok prepare(SmemT& sm, const uint4& rec, int g, int J, int tl) {
     Tok k;
     k.at = {bf_lo(rec.x), bf_hi(rec.x)};
     k.vg = {bf_lo(rec.y), bf_hi(rec.y)};
@@ -560,7 +564,7 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
     {
         const bool valid = cur.c * kC + tl < L;
         const uint4 first = valid ? __ldg(a.rec + rec_index(a, cur.b, cur.c, 0, cur.h0 + J, tl)) : zero4;
-        tk = prepare<kOutput>(sm, first, 0, J, tl);
+        tk = prepare(sm, first, 0, J, tl);
     }
     for (int g = 0; g < NS && !code; g++) {
         const uint32_t ph = g & 1;
@@ -749,7 +753,7 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
         // for first: prepare() arrives on the same barrier for the next step, and a wait must never be two
         // phases behind its barrier.
         if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 14; break; }
-        if (g + 1 < NS) tk = prepare<kOutput>(sm, rec, g + 1, J, tl);
+        if (g + 1 < NS) tk = prepare(sm, rec, g + 1, J, tl);
         TC4_STAMP(8);
         // ---- state hand-off: S <- BP S + K^T omega, column d = t of every head
         if (!warp_wait(&sm.mma_up, ph, ab)) { code = 15; break; }
@@ -793,6 +797,544 @@ __device__ __forceinline__ void compute(Smem<kOutput>& sm, const Args& a) {
         }
     }
     if (code && tl == 0) atomicCAS(a.status, 0, 200 + code);
+}
+
+// ==========================================================================================
+// Output pass, three thread blocks per SM.
+//
+// The output pass above is held to two blocks per SM by its three 32 KB tiles (K of this step, K of the
+// next, Q) and its 224 tensor-memory columns.  This variant lives on two tile buffers and 128 columns:
+//   * K of step g sits in tile[g & 1], Q of step g in the other buffer.  Q is only needed for the read-out
+//     side (P, rho, |q|), K for the solve (G, kappa) and the state update: once P, rho and |q| of step g are
+//     done, K of step g + 1 is fetched into Q's buffer (early enough for G of the next step), and once the
+//     state update of step g has completed, Q of step g + 1 is fetched into K's buffer (it lands a couple of
+//     thousand cycles into step g + 1, which is when the solve has been set up and P is needed).
+//   * G and P take turns in the same 64 columns (P is issued when every warp has its G row in registers),
+//     kappa and the state update share 32 columns (the update is read before the next states are published),
+//     rho has 32 of its own and is read after the substitution loop.
+//   * the states (operand of kappa / rho) and the omega columns (operand of the update) take turns in one
+//     small tile, so every token thread writes its whole omega column (its head's eight values and zeros).
+// ==========================================================================================
+struct __align__(1024) Smem3 {
+    uint8_t tile[2][kTile];
+    uint8_t so_tile[Cfg<true>::kSmallTile];
+    __nv_bfloat162 a[kC];
+    float2 bp[2][4];
+    uint64_t full_k, full_q, mma_g, mma_p, mma_k, mma_r, mma_up, g_free, p_free, r_free, s_ready, omega_ready,
+        bp_ready, drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr uint32_t k3TmemCols = 128, k3ColGP = 0, k3ColKU = 64, k3ColRho = 96;
+
+__device__ __forceinline__ void producer3(Smem3& sm, const CUtensorMap* tmK, const CUtensorMap* tmQ, const Args& a) {
+    using C = Cfg<true>;
+    volatile int* ab = &sm.abort_flag;
+    const uint32_t tm = sm.tmem_base;
+    constexpr uint32_t idesc_s = umma_idesc_bf16(128, C::kN, false, false);
+    constexpr uint32_t idesc64 = umma_idesc_bf16(128, 64, false, false);
+    constexpr uint32_t idesc_up = umma_idesc_bf16(128, C::kN, true, false);
+    const uint32_t taddr[2] = {smem_u32(sm.tile[0]), smem_u32(sm.tile[1])};
+    const uint32_t soaddr = smem_u32(sm.so_tile);
+    bool pend_k = false, pend_q = false;
+    int code = 0;
+    const int n_items = ((int)blockIdx.x < a.items) ? (a.items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int NS = n_items * kSteps;
+    auto load_tile = [&](uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, int g) {
+        const int item = (int)blockIdx.x + (g >> 2) * (int)gridDim.x;
+        const int h0 = (item % a.HG) * 4, c = (item / a.HG) % a.NC, b = item / (a.HG * a.NC);
+        const int l0 = c * kC + (g & 3) * kSub;
+        if (elect_one()) {
+            mbar_arrive_expect_tx(bar, kTile);
+#pragma unroll 1
+            for (int j = 0; j < 4; j++) {
+                tma_load_4d(dst + j * kSub * 128, tmap, bar, 0, h0 + j, l0, b);
+                tma_load_4d(dst + kSlab + j * kSub * 128, tmap, bar, 64, h0 + j, l0, b);
+            }
+        }
+        __syncwarp();
+    };
+    if (NS > 0) {
+        load_tile(sm.tile[0], tmK, &sm.full_k, 0); pend_k = true;
+        load_tile(sm.tile[1], tmQ, &sm.full_q, 0); pend_q = true;
+    }
+    const uint32_t lT[2] = {desc_lo(taddr[0], 16), desc_lo(taddr[1], 16)};        // K-major tile operands
+    const uint32_t lTt[2] = {desc_lo(taddr[0], kSlab), desc_lo(taddr[1], kSlab)}; // MN-major (state update)
+    const uint32_t lSO = desc_lo(soaddr, 16);
+    constexpr uint32_t kBigJump = (kSlab >> 4) - 8, kSmallJump = (C::kSmallSlab >> 4) - 8;
+    // UMMA groups issued (G, P, kappa, rho, state update) and the next tile loads (K / Q of step i_lk / i_lq)
+    int i_g = 0, i_p = 0, i_k = 0, i_r = 0, i_up = 0, i_lk = 1, i_lq = 1;
+    bool k_ok = false, q_ok = false;   // the K tile of step i_g / the Q tile of step i_p has landed
+    uint64_t last = global_ns();
+    uint32_t idle = 0;
+    auto par = [](int n) { return (uint32_t)(n & 1); };
+    while (i_up < NS) {
+        bool progress = false;
+        if (i_up < i_k && i_lq > i_up && warp_test(&sm.omega_ready, par(i_up))) {
+            // state update (issued only once the completion of the previous one has been observed by the Q
+            // reload below, so that mma_up is never more than one phase ahead of what this loop tests)
+            tc_fence_after();
+            uint32_t al = lTt[i_up & 1], bl = lSO;
+#pragma unroll 1
+            for (int j = 0; j < 8; j++) {
+                umma_lo_e(tm + k3ColKU, al, bl, idesc_up, j);
+                al += 2048 >> 4;
+                bl += (j == 3) ? 2 + kSmallJump : 2;
+            }
+            umma_commit_e(&sm.mma_up);
+            i_up++; progress = true;
+        } else if (i_k < i_g && warp_test(&sm.s_ready, par(i_k))) {
+            // kappa = K S^T (G of the step has been issued, so its K tile has landed)
+            tc_fence_after();
+            uint32_t ak = lT[i_k & 1], bl = lSO;
+#pragma unroll 1
+            for (int j = 0; j < 8; j++) {
+                umma_lo_e(tm + k3ColKU, ak, bl, idesc_s, j);
+                ak += (j == 3) ? 2 + kBigJump : 2;
+                bl += (j == 3) ? 2 + kSmallJump : 2;
+            }
+            umma_commit_e(&sm.mma_k);
+            i_k++; progress = true;
+        } else if (i_r < i_p && i_r < i_k && (i_r == 0 || warp_test(&sm.r_free, par(i_r - 1)))) {
+            // rho = Q S^T (P of the step has been issued: its Q tile has landed; kappa of the step has been
+            // issued: its states are published)
+            tc_fence_after();
+            uint32_t aq = lT[(i_r + 1) & 1], bl = lSO;
+#pragma unroll 1
+            for (int j = 0; j < 8; j++) {
+                umma_lo_e(tm + k3ColRho, aq, bl, idesc_s, j);
+                aq += (j == 3) ? 2 + kBigJump : 2;
+                bl += (j == 3) ? 2 + kSmallJump : 2;
+            }
+            umma_commit_e(&sm.mma_r);
+            i_r++; progress = true;
+        } else if (i_lq <= NS && i_lq <= i_up && warp_test(&sm.mma_up, par(i_lq - 1))) {
+            // the update of step n - 1 has completed: its K buffer takes the Q tile of step n
+            if (i_lq < NS) { load_tile(sm.tile[(i_lq + 1) & 1], tmQ, &sm.full_q, i_lq); pend_q = true; }
+            i_lq++; progress = true;
+        } else if (i_lk <= NS && i_lk <= i_r && i_lk <= i_p && warp_test(&sm.mma_r, par(i_lk - 1)) &&
+                   warp_test(&sm.mma_p, par(i_lk - 1)) && warp_test(&sm.p_free, par(i_lk - 1))) {
+            // P, rho and |q| of step n - 1 are done: its Q buffer takes the K tile of step n
+            if (i_lk < NS) { load_tile(sm.tile[i_lk & 1], tmK, &sm.full_k, i_lk); pend_k = true; }
+            i_lk++; progress = true;
+        } else {
+            if (i_p < NS && i_p < i_g) {   // P = Q K^T of step i_p into the columns its G has been read from
+                if (!q_ok && warp_test(&sm.full_q, par(i_p))) { q_ok = true; pend_q = false; }
+                if (q_ok && warp_test(&sm.g_free, par(i_p))) {
+                    tc_fence_after();
+                    uint32_t ak = lT[i_p & 1], aq = lT[(i_p + 1) & 1];
+                    constexpr uint32_t r2 = 2 * (kSub * 128 >> 4), all = 0xffffffffu;
+#pragma unroll 1
+                    for (int j = 0; j < 8; j++) {
+                        umma_lo_unit_e(tm + k3ColGP, aq, ak, idesc64, j, 0u, 0u, all, all);
+                        umma_lo_unit_e(tm + k3ColGP, aq, ak + r2, idesc64, j, all, all, 0u, 0u);
+                        const uint32_t big = (j == 3) ? 2 + kBigJump : 2;
+                        ak += big;
+                        aq += big;
+                    }
+                    umma_commit_e(&sm.mma_p);
+                    i_p++; q_ok = false; progress = true;
+                }
+            }
+            if (!progress && i_g < NS) {   // G = K K^T of step i_g into the columns the previous P has been read from
+                if (!k_ok && warp_test(&sm.full_k, par(i_g))) { k_ok = true; pend_k = false; }
+                if (k_ok && (i_g == 0 || warp_test(&sm.p_free, par(i_g - 1)))) {
+                    tc_fence_after();
+                    uint32_t ak = lT[i_g & 1];
+                    constexpr uint32_t r2 = 2 * (kSub * 128 >> 4), all = 0xffffffffu;
+#pragma unroll 1
+                    for (int j = 0; j < 8; j++) {
+                        umma_lo_unit_e(tm + k3ColGP, ak, ak, idesc64, j, 0u, 0u, all, all);
+                        umma_lo_unit_e(tm + k3ColGP, ak, ak + r2, idesc64, j, all, all, 0u, 0u);
+                        ak += (j == 3) ? 2 + kBigJump : 2;
+                    }
+                    umma_commit_e(&sm.mma_g);
+                    i_g++; k_ok = false; progress = true;
+                }
+            }
+        }
+        if (progress) {
+            last = global_ns();
+        } else if ((++idle & 7) != 0) {
+            __nanosleep(200);
+        } else if (__any_sync(0xffffffffu, *ab || global_ns() - last > kWaitLimitNs)) {
+            code = 1 + (i_g > i_k) + 2 * (i_k > i_up);
+            *ab = 1;
+            break;
+        }
+    }
+    if (code && elect_one()) {   // the lane that issued the UMMAs and the TMA loads
+        atomicCAS(a.status, 0, 400 + code);
+        umma_commit(&sm.drain);
+        int never = 0;
+        mbar_wait(&sm.drain, 0, &never);
+        if (pend_k) mbar_wait(&sm.full_k, 0, &never), mbar_wait(&sm.full_k, 1, &never);
+        if (pend_q) mbar_wait(&sm.full_q, 0, &never), mbar_wait(&sm.full_q, 1, &never);
+    }
+    __syncwarp();
+}
+
+// The explicit walk for this variant: G and P arrive one after the other in the same columns, so it reports
+// G as read after phase A and waits for P before phase C.
+__device__ __forceinline__ BlockOut robust_block3(Smem3& sm, uint32_t tcol, uint32_t ph, int J, int tl, cplx at, cplx vg,
+                                                  float be, float nt, cplx kz, cplx kr) {
+    volatile int* ab = &sm.abort_flag;
+    const float bnn = be * nt * nt;
+    cplx W = at, S = at;   // inclusive prefix / suffix products of a over the sub-block
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        cplx up = {__shfl_up_sync(0xffffffffu, W.r, o), __shfl_up_sync(0xffffffffu, W.i, o)};
+        cplx dn = {__shfl_down_sync(0xffffffffu, S.r, o), __shfl_down_sync(0xffffffffu, S.i, o)};
+        if (tl >= o) W = cmul(W, up);
+        if (tl + o < 32) S = cmul(S, dn);
+    }
+    cplx W0 = {__shfl_up_sync(0xffffffffu, W.r, 1), __shfl_up_sync(0xffffffffu, W.i, 1)};
+    if (tl == 0) W0 = {1.f, 0.f};
+    cplx V = {__shfl_down_sync(0xffffffffu, S.r, 1), __shfl_down_sync(0xffffffffu, S.i, 1)};
+    if (tl == 31) V = {1.f, 0.f};
+    cplx cc[32];   // run-time indexed on purpose: local memory (see robust_block)
+    {
+        cplx cur = {1.f, 0.f};
+#pragma unroll 1
+        for (int grp = 3; grp >= 0; grp--) {
+            float g8[8];
+            tmem_ld8(tcol + grp * 8, g8);
+#pragma unroll
+            for (int e = 7; e >= 0; e--) {
+                const int i = grp * 8 + e;
+                const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
+                const bool on = i < tl;
+                const cplx fg = cmul(at, cur);
+                cc[i] = {on ? fg.r * g8[e] : 0.f, on ? fg.i * g8[e] : 0.f};
+                const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+                cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+            }
+        }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (tl == 0) mbar_arrive(&sm.g_free);
+    const cplx wkz = cmul(W, kz), wkr = cmul(W, kr);
+    cplx cw = {nt * be * (vg.r - nt * wkz.r), nt * be * (vg.i - nt * wkz.i)};
+    cplx cx = {nt * be * nt * wkr.r, nt * be * nt * wkr.i};
+#pragma unroll 1
+    for (int grp = 0; grp < 4; grp++) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int i = grp * 8 + e;
+            const float cr_ = bnn * cc[i].r, ci_ = bnn * cc[i].i;
+            const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+            cw.r -= cr_ * uw.r - ci_ * uw.i;
+            cw.i -= cr_ * uw.i + ci_ * uw.r;
+            cx.r -= cr_ * ux.r - ci_ * ux.i;
+            cx.i -= cr_ * ux.i + ci_ * ux.r;
+        }
+    }
+    BlockOut o;
+    o.wh = cmul(V, cw);
+    const cplx xv = cmul(V, cx);
+    o.xh = {-xv.r, -xv.i};
+    o.ysum = {0.f, 0.f};
+    o.pd = 0.f;
+    o.ok = warp_wait(&sm.mma_p, ph, ab);
+    if (!o.ok) return o;
+    tc_fence_after();
+    cplx yin = {0.f, 0.f};
+    float pd = 0.f;
+    cplx cur = {1.f, 0.f};
+#pragma unroll 1
+    for (int grp = 3; grp >= 0; grp--) {
+        float p8[8];
+        tmem_ld8(tcol + grp * 8, p8);
+#pragma unroll
+        for (int e = 7; e >= 0; e--) {
+            const int i = grp * 8 + e;
+            const float2 ai = __bfloat1622float2(sm.a[J * 32 + i]);
+            const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+            const bool on = i < tl;
+            pd = (i == tl) ? p8[e] : pd;
+            const cplx au = cmul(at, uw);
+            const cplx ee = cmul(cur, cplx{au.r - ux.r, au.i - ux.i});
+            const float pi = on ? p8[e] : 0.f;
+            yin.r += pi * ee.r;
+            yin.i += pi * ee.i;
+            const cplx nx = cmul(cur, cplx{ai.x, ai.y});
+            cur = {on ? nx.r : cur.r, on ? nx.i : cur.i};
+        }
+    }
+    // W rho_z + W0 rho_r is added by the caller, which reads rho after this walk
+    o.ysum = {pd * cw.r + yin.r, pd * cw.i + yin.i};
+    o.pd = pd;
+    // the caller needs W and W0 for that: hand them back in place of the unused fields
+    o.W = W;
+    o.W0 = W0;
+    return o;
+}
+
+__device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
+    using C = Cfg<true>;
+    volatile int* ab = &sm.abort_flag;
+    const int t = threadIdx.x, J = t >> 5, tl = t & 31;
+    const int H = a.H, L = a.L;
+    const uint32_t tlane = sm.tmem_base + ((uint32_t)(J * 32) << 16);
+    const uint32_t tcol = tlane + k3ColGP + 32 * (J & 1);
+    const int n_items = ((int)blockIdx.x < a.items) ? (a.items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int NS = n_items * kSteps;
+    if (NS == 0) return;
+    int code = 0;
+    cplx Sz[4], Sr[4];
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    ItemPos cur = item_pos(a, blockIdx.x), nxi = cur;
+    Tok tk;
+    {
+        const bool valid = cur.c * kC + tl < L;
+        const uint4 first = valid ? __ldg(a.rec + rec_index(a, cur.b, cur.c, 0, cur.h0 + J, tl)) : zero4;
+        tk = prepare(sm, first, 0, J, tl);
+    }
+    for (int g = 0; g < NS && !code; g++) {
+        const uint32_t ph = g & 1;
+        const int step = g & 3;
+        if (step == 0) {
+            if (g > 0) cur = nxi;
+            nxi = item_pos(a, (int)blockIdx.x + ((g >> 2) + 1) * (int)gridDim.x);
+        }
+        const int l = cur.c * kC + step * kSub + tl, hd = cur.h0 + J;
+        const bool valid = l < L;
+        const size_t unit0 = ((size_t)cur.b * a.NC + cur.c) * H + cur.h0;   // workspace slot of head h0
+        if (step == 0) {   // states at the chunk start, column d = t of every head
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float* s = a.ws_state + (unit0 + u) * 2 * kD;
+                Sz[u] = {0.f, 0.f};
+                Sr[u] = {s[t], s[kD + t]};
+            }
+        }
+        // ---- publish the states for kappa / rho of this step (the omega columns of the previous step have
+        // been consumed: this thread has seen its state update complete)
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 0, t, Sz[u].r);
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 2, t, Sz[u].i);
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 4, t, Sr[u].r);
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 6, t, Sr[u].i);
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (tl == 0) mbar_arrive(&sm.s_ready);
+        // ---- fetch the record of step g + 1 (the next item's first sub-block after this item's last)
+        uint4 rec = zero4;
+        if (g + 1 < NS) {
+            const ItemPos& np = (step + 1 < kSteps) ? cur : nxi;
+            const int nsub = (step + 1) & 3;
+            if (np.c * kC + nsub * kSub + tl < L) rec = __ldg(a.rec + rec_index(a, np.b, np.c, nsub, np.h0 + J, tl));
+        }
+        const cplx at = tk.at, vg = tk.vg;
+        const float be = tk.be;
+        // ---- Gram row of the own head: |k_t|^-1 from its diagonal
+        if (!warp_wait(&sm.mma_g, ph, ab)) { code = 13; break; }
+        tc_fence_after();
+        float gs[32], p[32];
+        float pd = 0.f, mt = 0.f;
+        tmem_ld32(tcol, gs);
+        if (tk.fast) {   // G is in registers: P may take its columns (the explicit walk reads G again itself)
+            tc_fence_before();
+            __syncwarp();
+            if (tl == 0) mbar_arrive(&sm.g_free);
+        }
+        float gd = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) gd = (i == tl) ? gs[i] : gd;
+        const float nt = rsqrtf(gd + kEps);
+        const float bnn = be * nt * nt;
+        // ---- kappa_t = k_t . z0 | r0 (raw rows; hi + lo parts summed)
+        if (!warp_wait(&sm.mma_k, ph, ab)) { code = 12; break; }
+        tc_fence_after();
+        float k8[8];
+        tmem_ld8(tlane + k3ColKU + 8 * J, k8);
+        const cplx kz = {k8[0] + k8[1], k8[2] + k8[3]}, kr = {k8[4] + k8[5], k8[6] + k8[7]};
+        BlockOut o;
+        cplx yW = {0.f, 0.f}, yW0 = {0.f, 0.f};   // factors of rho_z and rho_r in the read-out
+        if (tk.fast) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) gs[i] = (i < tl) ? -bnn * gs[i] : 0.f;
+            const cplx rkz = cmul(tk.R, kz), rkr = cmul(tk.R, kr);
+            cplx cw = {nt * be * (tk.viw.r - nt * rkz.r), nt * be * (tk.viw.i - nt * rkz.i)};
+            cplx cx = {nt * be * nt * rkr.r, nt * be * nt * rkr.i};
+            // ---- |q_t|^-1 from the Q tile row (swizzled 16-byte pieces); the Q tile lands late in this variant
+            if (!warp_wait(&sm.full_q, ph, ab)) { code = 11; break; }
+            {
+                const uint8_t* qt = sm.tile[(g + 1) & 1];
+                float qq = 0.f;
+#pragma unroll
+                for (int sl = 0; sl < 2; sl++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint4 r = *reinterpret_cast<const uint4*>(qt + sl * kSlab + t * 128 + ((j ^ (t & 7)) << 4));
+                        float f[8];
+                        unpack8(r, f);
+#pragma unroll
+                        for (int e = 0; e < 8; e++) qq = fmaf(f[e], f[e], qq);
+                    }
+                mt = rsqrtf(qq + kEps);
+            }
+            if (!warp_wait(&sm.mma_p, ph, ab)) { code = 16; break; }
+            tc_fence_after();
+            tmem_ld32(tcol, p);
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                pd = (i == tl) ? p[i] : pd;
+                p[i] = (i < tl) ? p[i] : 0.f;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (tl == 0) mbar_arrive(&sm.p_free);   // P is in registers, |q| has been taken from the Q tile
+            cplx accu = {0.f, 0.f}, accx = {0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const cplx uw = cshfl(cw, i), ux = cshfl(cx, i);
+                cw.r = fmaf(gs[i], uw.r, cw.r);
+                cw.i = fmaf(gs[i], uw.i, cw.i);
+                cx.r = fmaf(gs[i], ux.r, cx.r);
+                cx.i = fmaf(gs[i], ux.i, cx.i);
+                accu.r = fmaf(p[i], uw.r, accu.r);
+                accu.i = fmaf(p[i], uw.i, accu.i);
+                accx.r = fmaf(p[i], ux.r, accx.r);
+                accx.i = fmaf(p[i], ux.i, accx.i);
+            }
+            o.wh = cmul(tk.D31, cw);
+            const cplx xv = cmul(tk.D31, cx);
+            o.xh = {-xv.r, -xv.i};
+            // y = D (R rho_z + pd u^ + accu) + D0 (R rho_r - accx); lane 0: W0 = 1, the carried correction itself
+            const cplx yl = cmul(tk.D, cplx{pd * cw.r + accu.r, pd * cw.i + accu.i});
+            cplx yc = cmul(tk.D0, cplx{-accx.r, -accx.i});
+            if (tl == 0) yc = {0.f, 0.f};
+            o.ysum = {yl.r + yc.r, yl.i + yc.i};
+            yW = cmul(tk.D, tk.R);
+            yW0 = cmul(tk.D0, tk.R);
+            if (tl == 0) yW0 = {1.f, 0.f};
+        } else {
+            if (!warp_wait(&sm.full_q, ph, ab)) { code = 11; break; }
+            {
+                const uint8_t* qt = sm.tile[(g + 1) & 1];
+                float qq = 0.f;
+#pragma unroll 1
+                for (int c16 = 0; c16 < 16; c16++) {
+                    const uint4 r = *reinterpret_cast<const uint4*>(qt + (c16 >> 3) * kSlab + t * 128 + (((c16 & 7) ^ (t & 7)) << 4));
+                    float f[8];
+                    unpack8(r, f);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) qq = fmaf(f[e], f[e], qq);
+                }
+                mt = rsqrtf(qq + kEps);
+            }
+            o = robust_block3(sm, tcol, ph, J, tl, at, vg, be, nt, kz, kr);
+            if (!o.ok) { code = 17; break; }
+            pd = o.pd;
+            yW = o.W;
+            yW0 = o.W0;
+            tc_fence_before();
+            __syncwarp();
+            if (tl == 0) mbar_arrive(&sm.p_free);
+        }
+        // ---- rho_t = q_t . z0 | r0; once it has completed, nothing reads the published states any more and
+        // the tile can take the omega columns
+        if (!warp_wait(&sm.mma_r, ph, ab)) { code = 18; break; }
+        tc_fence_after();
+        float r8[8];
+        tmem_ld8(tlane + k3ColRho + 8 * J, r8);
+        tc_fence_before();
+        __syncwarp();
+        if (tl == 0) mbar_arrive(&sm.r_free);
+        // ---- omega column of this token: the head's eight values, zeros in the other heads' rows
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const bool mine = u == J;
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 0, t, mine ? o.wh.r : 0.f);
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 2, t, mine ? o.wh.i : 0.f);
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 4, t, mine ? o.xh.r : 0.f);
+            st_hi_lo(sm.so_tile, C::kSmallSlab, 8 * u + 6, t, mine ? o.xh.i : 0.f);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (tl == 0) mbar_arrive(&sm.omega_ready);
+        {
+            const cplx rz = cmul(yW, cplx{r8[0] + r8[1], r8[2] + r8[3]});
+            const cplx rr = cmul(yW0, cplx{r8[4] + r8[5], r8[6] + r8[7]});
+            float yr = mt * (o.ysum.r + rz.r + rr.r), yi = mt * (o.ysum.i + rz.i + rr.i);
+            if (a.shortcut_scale != 0.f) {   // block.py:202-208
+                const float qk = mt * nt * pd;
+                yr += a.shortcut_scale * qk * qk * vg.r;
+                yi += a.shortcut_scale * qk * qk * vg.i;
+            }
+            if (valid) {
+                __nv_bfloat162 ov = __floats2bfloat162_rn(bfr(yr) * tk.sc, bfr(yi) * tk.sc);
+                *reinterpret_cast<__nv_bfloat162*>(a.y + (((size_t)cur.b * L + l) * H + hd) * 2) = ov;
+            }
+        }
+        // ---- the next step's token while the state-update UMMA runs (this step's block products are waited for
+        // first: prepare() arrives on the same barrier for the next step)
+        if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 14; break; }
+        if (g + 1 < NS) tk = prepare(sm, rec, g + 1, J, tl);
+        // ---- state hand-off: S <- W_31 S + K^T omega, column d = t of every head
+        if (!warp_wait(&sm.mma_up, ph, ab)) { code = 15; break; }
+        tc_fence_after();
+        if (step + 1 < kSteps) {
+            float up[32];
+            tmem_ld32(tlane + k3ColKU, up);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const cplx bpu = {sm.bp[ph][u].x, sm.bp[ph][u].y};
+                const cplx nz = cmul(bpu, Sz[u]), nr = cmul(bpu, Sr[u]);
+                Sz[u] = {nz.r + up[8 * u] + up[8 * u + 1], nz.i + up[8 * u + 2] + up[8 * u + 3]};
+                Sr[u] = {nr.r + up[8 * u + 4] + up[8 * u + 5], nr.i + up[8 * u + 6] + up[8 * u + 7]};
+            }
+        }
+        tc_fence_before();
+    }
+    if (code && tl == 0) atomicCAS(a.status, 0, 500 + code);
+}
+
+__global__ void __launch_bounds__(kThreads, 3)
+scan_tc4_out3_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ, const Args a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    Smem3& sm = *reinterpret_cast<Smem3*>(smem_raw);
+    const int warp = threadIdx.x >> 5;
+    if ((smem_u32(smem_raw) & 1023u) != 0) {   // the swizzled tiles need 1024-byte alignment
+        if (threadIdx.x == 0) atomicCAS(a.status, 0, 399);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.full_k, 1); mbar_init(&sm.full_q, 1);
+        mbar_init(&sm.mma_g, 1); mbar_init(&sm.mma_p, 1); mbar_init(&sm.mma_k, 1); mbar_init(&sm.mma_r, 1);
+        mbar_init(&sm.mma_up, 1);
+        mbar_init(&sm.g_free, 4); mbar_init(&sm.p_free, 4); mbar_init(&sm.r_free, 4);
+        mbar_init(&sm.s_ready, 4); mbar_init(&sm.omega_ready, 4); mbar_init(&sm.bp_ready, 4);
+        mbar_init(&sm.drain, 1);
+        sm.abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 4) tmem_alloc(&sm.tmem_base, k3TmemCols);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp < 4) {
+        compute3(sm, a);
+    } else {
+        if (threadIdx.x == 128) {
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmQ);
+        }
+        __syncwarp();
+        producer3(sm, &tmK, &tmQ, a);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        __syncwarp();
+        tmem_dealloc(sm.tmem_base, k3TmemCols);
+    }
 }
 
 template <bool kOutput>
@@ -946,10 +1488,11 @@ int scan_tc4_dynamics(const void* v, const void* gate_raw, const float* log_dt_s
 }
 
 // One pass of the four-chain tensor-core scan over every chunk.  output = false: local pass (fills
-// ws_state / ws_gamma for the carry pass); output = true: reads the carries from ws_state, writes y.
+// ws_state / ws_gamma for the carry pass); output = true: reads the carries from ws_state, writes y
+// (two_blocks: the variant with three tile buffers and two blocks per SM).
 // status: one int in device memory, set by a bounded wait that ran out (not cleared here).
-int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, float* ws_gamma, float* ws_state,
-                  void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st) {
+int scan_tc4_pass(bool output, bool two_blocks, const void* q, const void* k, const void* rec, float* ws_gamma,
+                  float* ws_state, void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st) {
     using namespace tc4;
     CUtensorMap tmK, tmQ;
     if (!make_tile_map(&tmK, k, B, L, H) || !make_tile_map(&tmQ, output ? q : k, B, L, H)) return CDSSM_ERR_CUDA;
@@ -966,6 +1509,9 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
             return rc;
         if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                      (int)sizeof(Smem<false>))))
+            return rc;
+        if (int rc = check_cuda(cudaFuncSetAttribute(scan_tc4_out3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     (int)sizeof(Smem3))))
             return rc;
         int n = 0;
         if (int rc = check_cuda(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev))) return rc;
@@ -988,9 +1534,11 @@ int scan_tc4_pass(bool output, const void* q, const void* k, const void* rec, fl
     const long long items = (long long)B * a.NC * a.HG;
     if (items > 0x7fffffff / 8) return CDSSM_ERR_UNSUPPORTED;
     a.items = (int)items;
-    const long long resident = (long long)(output ? Cfg<true>::kBlocksPerSm : Cfg<false>::kBlocksPerSm) * sms;
+    const bool three = output && !two_blocks;   // the output pass on two tile buffers, three blocks per SM
+    const long long resident = (long long)(!output ? Cfg<false>::kBlocksPerSm : three ? 3 : Cfg<true>::kBlocksPerSm) * sms;
     const int grid = (int)(items < resident ? items : resident);
-    if (output) scan_tc4_kernel<true><<<grid, kThreads, smem, st>>>(tmK, tmQ, a);
+    if (three) scan_tc4_out3_kernel<<<grid, kThreads, sizeof(Smem3), st>>>(tmK, tmQ, a);
+    else if (output) scan_tc4_kernel<true><<<grid, kThreads, smem, st>>>(tmK, tmQ, a);
     else scan_tc4_kernel<false><<<grid, kThreads, smem, st>>>(tmK, tmQ, a);
     return check_launch();
 }
