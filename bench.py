@@ -469,14 +469,14 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                              "kernel": ("scan_tc_kernel (single pass)" if args.flags & 2 else
-                                        "the whole step (tc4_dynamics + scan_tc4 local pass + scan_carry + scan_tc4 "
+                                        "the whole step (tc4_dynamics + scan_tc4 local pass + scan_carry + scan_tc4_out3 "
                                         "output pass)" if uses_tc4 else
                                         "the whole step (scan_walk local pass + scan_carry + scan_walk output pass)"),
                              "algorithmic_bytes_per_launch": abytes}}
         if "tc4_output_ms" in extra:
             out_ms = extra["tc4_output_ms"]
             line["roofline"]["dominant_kernel"] = {
-                "name": "tc4::scan_tc4_kernel<true> (output pass)", "ms": out_ms,
+                "name": "tc4::scan_tc4_out3_kernel (output pass)", "ms": out_ms,
                 "achieved": abytes / (out_ms / 1e3) / 1e9, "frac": abytes / (out_ms / 1e3) / 1e9 / peak,
                 "how": "a call that reuses the local pass in the workspace (records pre-pass + carry pass + output "
                        "pass), CUDA-event timed; algorithmic bytes of the whole step"}

@@ -1122,6 +1122,7 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
         tc_fence_before();
         __syncwarp();
         if (tl == 0) mbar_arrive(&sm.s_ready);
+        TC4_STAMP(0);
         // ---- fetch the record of step g + 1 (the next item's first sub-block after this item's last)
         uint4 rec = zero4;
         if (g + 1 < NS) {
@@ -1132,8 +1133,10 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
         const cplx at = tk.at, vg = tk.vg;
         const float be = tk.be;
         // ---- Gram row of the own head: |k_t|^-1 from its diagonal
+        TC4_STAMP(2);
         if (!warp_wait(&sm.mma_g, ph, ab)) { code = 13; break; }
         tc_fence_after();
+        TC4_STAMP(3);
         float gs[32], p[32];
         float pd = 0.f, mt = 0.f;
         tmem_ld32(tcol, gs);
@@ -1150,6 +1153,7 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
         // ---- kappa_t = k_t . z0 | r0 (raw rows; hi + lo parts summed)
         if (!warp_wait(&sm.mma_k, ph, ab)) { code = 12; break; }
         tc_fence_after();
+        TC4_STAMP(4);
         float k8[8];
         tmem_ld8(tlane + k3ColKU + 8 * J, k8);
         const cplx kz = {k8[0] + k8[1], k8[2] + k8[3]}, kr = {k8[4] + k8[5], k8[6] + k8[7]};
@@ -1162,7 +1166,9 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
             cplx cw = {nt * be * (tk.viw.r - nt * rkz.r), nt * be * (tk.viw.i - nt * rkz.i)};
             cplx cx = {nt * be * nt * rkr.r, nt * be * nt * rkr.i};
             // ---- |q_t|^-1 from the Q tile row (swizzled 16-byte pieces); the Q tile lands late in this variant
+            TC4_STAMP(9);
             if (!warp_wait(&sm.full_q, ph, ab)) { code = 11; break; }
+            TC4_STAMP(10);
             {
                 const uint8_t* qt = sm.tile[(g + 1) & 1];
                 float qq = 0.f;
@@ -1178,8 +1184,10 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
                     }
                 mt = rsqrtf(qq + kEps);
             }
+            TC4_STAMP(12);
             if (!warp_wait(&sm.mma_p, ph, ab)) { code = 16; break; }
             tc_fence_after();
+            TC4_STAMP(13);
             tmem_ld32(tcol, p);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
@@ -1239,6 +1247,7 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
         }
         // ---- rho_t = q_t . z0 | r0; once it has completed, nothing reads the published states any more and
         // the tile can take the omega columns
+        TC4_STAMP(5);
         if (!warp_wait(&sm.mma_r, ph, ab)) { code = 18; break; }
         tc_fence_after();
         float r8[8];
@@ -1274,11 +1283,14 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
         }
         // ---- the next step's token while the state-update UMMA runs (this step's block products are waited for
         // first: prepare() arrives on the same barrier for the next step)
+        TC4_STAMP(1);
         if (!warp_wait(&sm.bp_ready, ph, ab)) { code = 14; break; }
         if (g + 1 < NS) tk = prepare(sm, rec, g + 1, J, tl);
         // ---- state hand-off: S <- W_31 S + K^T omega, column d = t of every head
+        TC4_STAMP(8);
         if (!warp_wait(&sm.mma_up, ph, ab)) { code = 15; break; }
         tc_fence_after();
+        TC4_STAMP(6);
         if (step + 1 < kSteps) {
             float up[32];
             tmem_ld32(tlane + k3ColKU, up);
@@ -1291,6 +1303,7 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
             }
         }
         tc_fence_before();
+        TC4_STAMP(7);
     }
     if (code && tl == 0) atomicCAS(a.status, 0, 500 + code);
 }
