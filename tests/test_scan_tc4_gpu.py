@@ -1,6 +1,7 @@
 """The four-chain tcgen05/TMA scan kernels (bf16, N = 2, D = C = 128, H % 4 == 0) against the CPU oracle
 and against the CUDA-core kernels, through the C ABI.  Flag bits 256 / 512 keep the CUDA-core local /
-output pass, so each tensor-core pass is also checked on its own."""
+output pass, so each tensor-core pass is also checked on its own; bit 1024 selects the output pass with
+three tile buffers (two thread blocks per SM) instead of the default one."""
 import numpy as np
 import pytest
 import torch
@@ -10,7 +11,7 @@ from util import BF16_TOL, rel_err, to_np
 
 pytestmark = pytest.mark.gpu
 N, C, D = 2, 128, 128
-KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT = 256, 512
+KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT, TWO_BLOCK_OUTPUT = 256, 512, 1024
 
 
 def _inputs(orc, B, H, L, seed, scale=True):
@@ -21,7 +22,7 @@ def _inputs(orc, B, H, L, seed, scale=True):
     return inp
 
 
-@pytest.mark.parametrize("extra", [KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT, 0])
+@pytest.mark.parametrize("extra", [KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT, 0, TWO_BLOCK_OUTPUT])
 @pytest.mark.parametrize("B,H,L", [(1, 4, 128), (1, 4, 256), (2, 8, 300), (1, 4, 1), (1, 4, 129), (2, 12, 1024),
                                    (3, 32, 512)])
 def test_tc4_matches_oracle_and_simt(ops, orc, B, H, L, extra):
