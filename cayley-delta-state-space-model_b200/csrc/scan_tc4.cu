@@ -1171,18 +1171,16 @@ __device__ __forceinline__ void compute3(Smem3& sm, const Args& a) {
             TC4_STAMP(10);
             {
                 const uint8_t* qt = sm.tile[(g + 1) & 1];
-                float qq = 0.f;
+                float qq = 0.f, qq2 = 0.f;
+#pragma unroll 2
+                for (int c16 = 0; c16 < 16; c16++) {
+                    const uint4 r = *reinterpret_cast<const uint4*>(qt + (c16 >> 3) * kSlab + t * 128 + (((c16 & 7) ^ (t & 7)) << 4));
+                    float f[8];
+                    unpack8(r, f);
 #pragma unroll
-                for (int sl = 0; sl < 2; sl++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint4 r = *reinterpret_cast<const uint4*>(qt + sl * kSlab + t * 128 + ((j ^ (t & 7)) << 4));
-                        float f[8];
-                        unpack8(r, f);
-#pragma unroll
-                        for (int e = 0; e < 8; e++) qq = fmaf(f[e], f[e], qq);
-                    }
-                mt = rsqrtf(qq + kEps);
+                    for (int e = 0; e < 4; e++) { qq = fmaf(f[e], f[e], qq); qq2 = fmaf(f[4 + e], f[4 + e], qq2); }
+                }
+                mt = rsqrtf(qq + qq2 + kEps);
             }
             TC4_STAMP(12);
             if (!warp_wait(&sm.mma_p, ph, ab)) { code = 16; break; }
