@@ -739,6 +739,14 @@ int scan_tc4_dynamics(const void* v, const void* gate_raw, const float* log_dt_s
                       void* rec, const DynConsts& dc, int B, int L, int H, int pos0, int segs, cudaStream_t st);
 int scan_tc4_pass(bool output, bool two_blocks, const void* q, const void* k, const void* rec, float* ws_gamma,
                   float* ws_state, void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st);
+// scan_wa.cu
+bool scan_wa_supported(int D, int N, int C, int H, int dtype);
+size_t scan_wa_record_bytes(int B, int L, int H, int C);
+int scan_wa_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
+                     void* rec, const DynConsts& dc, int B, int L, int H, int C, int pos0, int segs, cudaStream_t st);
+int scan_wa_pass(bool output, const void* q, const void* k, const void* rec, float* ws_gamma, float* ws_state, void* y,
+                 int* status, float shortcut_scale, int B, int L, int H, int D, unsigned long long wait_ns, int withhold,
+                 cudaStream_t st);
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -749,7 +757,7 @@ extern "C" size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int
     const size_t units = (size_t)B * NC * H * (N / 2);
     size_t bytes = 256 + align256(units * 2 * sizeof(float)) + align256(units * 2 * D * sizeof(float));
     // per-token records of the four-chain tensor-core kernels (the data type is not known here)
-    if (scan_tc4_supported(D, N, C, H, CDSSM_BF16)) bytes += align256(scan_tc4_record_bytes(B, L, H));
+    if (scan_wa_supported(D, N, C, H, CDSSM_BF16)) bytes += align256(scan_wa_record_bytes(B, L, H, C));
     return bytes;
 }
 
@@ -827,6 +835,27 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     // them: measured faster than the CUDA-core walks at every size tried on B200 (2.7x at 64 chunk-head-groups,
     // 1.2x at 4096), so they are taken whenever the shapes allow and nothing else was asked for.  (Bits 256 /
     // 512 keep the CUDA-core local / output pass: used by the tests to check each tensor-core pass alone.)
+    // Warp-autonomous tensor-core passes (scan_wa.cu): the default wherever the shapes allow.
+    const bool wa_ok = tail_state == nullptr && scan_wa_supported(D, N, C, H, dtype);
+    const bool wa_asked = (flags & CDSSM_SCAN_TENSOR_CORE_WA) != 0;
+    if (!(flags & (CDSSM_SCAN_FORCE_SIMT | CDSSM_SCAN_TENSOR_CORE4)) && (wa_asked || wa_ok)) {
+        if (!wa_ok) return CDSSM_ERR_UNSUPPORTED;
+        cudaStream_t st = (cudaStream_t)stream;
+        const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
+        void* rec = reinterpret_cast<char*>(a.ws_state) + align256((size_t)a.units * 2 * D * sizeof(float));
+        if (int rc = scan_wa_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, C, pos0, segs, st))
+            return rc;
+        if (a.run_local && tc_local) {
+            if (int rc = scan_wa_pass(false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale, B, L, H,
+                                      D, 0, 0, st))
+                return rc;
+            a.run_local = 0;
+        }
+        a.run_output = tc_output ? 0 : 1;
+        if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;   // carry pass (+ whatever was kept)
+        if (!tc_output || summary_only) return CDSSM_OK;
+        return scan_wa_pass(true, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L, H, D, 0, 0, st);
+    }
     const bool tc4_ok = tail_state == nullptr && scan_tc4_supported(D, N, C, H, dtype);
     const bool tc4_asked = (flags & CDSSM_SCAN_TENSOR_CORE4) != 0;
     if (!(flags & CDSSM_SCAN_FORCE_SIMT) && (tc4_asked || tc4_ok)) {

@@ -239,4 +239,127 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float* r) {
                  : "r"(taddr)
                  : "memory");
 }
+// Bounded wait with the limit as an argument (nanoseconds of the global timer).
+__device__ __forceinline__ bool mbar_wait_ns(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                             uint64_t limit_ns) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
+        if (mbar_test(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+#pragma unroll 1
+    for (uint32_t i = 0;; i++) {
+        if (mbar_test(bar, parity)) return true;
+        __nanosleep(32);
+        if ((i & 31) == 31) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > limit_ns) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// Bounded wait that suspends the warp in hardware instead of spinning: mbarrier.try_wait blocks for an
+// implementation-defined time and returns early when the phase completes, so a waiting warp leaves the issue
+// slots to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_nohint(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_suspend(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint64_t limit_ns) {
+    if (mbar_try_wait_nohint(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+#pragma unroll 1
+    for (uint32_t i = 0;; i++) {
+        if (mbar_try_wait_nohint(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > limit_ns) break;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// ---- UMMA issue from a whole warp (one elected lane issues; the operands stay warp-uniform) ----
+// Every shared-memory descriptor of the 128-byte-swizzled tiles has the same upper word (stride between
+// eight-row groups 1024 bytes, Blackwell descriptor version, 128-byte swizzle); only the lower word (start
+// address and leading-dimension offset, both in 16-byte units) is carried around and advanced.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+// D[tmem] (+)= A B with the output restricted to the TMEM lanes whose bit in {m0..m3} is CLEAR.
+__device__ __forceinline__ void umma_bf16_masked_elect(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                       uint32_t acc, uint32_t m0, uint32_t m1, uint32_t m2,
+                                                       uint32_t m3) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 ad, bd;\n\t"
+        "mov.b64 ad, {%1, %9};\n\t"
+        "mov.b64 bd, {%2, %9};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(acc), "r"(m0), "r"(m1), "r"(m2), "r"(m3),
+          "r"(kDescHiSw128)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_elect(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 ad, bd;\n\t"
+        "mov.b64 ad, {%1, %5};\n\t"
+        "mov.b64 bd, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(acc), "r"(kDescHiSw128)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t e;
+    asm volatile(
+        "{\n\t.reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, e;\n\t}"
+        : "=r"(e));
+    return e != 0;
+}
+
+// ---- warp-level matrix instructions (the skinny products with the running state) ---------------
+// Four 8x8 bf16 matrices from shared memory; lane l supplies the address of row (l & 7) of matrix (l >> 3).
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+// d (16 x 8, fp32) += a (16 x 16, bf16, row-major fragment) * b (16 x 8, bf16, column-major fragment)
+__device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 }  // namespace sm100

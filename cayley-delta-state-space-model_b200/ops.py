@@ -200,6 +200,7 @@ TENSOR_CORE = 2
 REUSE_LOCAL = 8
 EXACT = 32
 TENSOR_CORE4 = 64
+TENSOR_CORE_WA = 128
 
 _workspaces = {}
 

@@ -106,6 +106,11 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
                                       N = 2, D = C = 128, H a multiple of 4 and no tail_state):
                                       CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
 
+#define CDSSM_SCAN_TENSOR_CORE_WA 128 /* insist on the warp-autonomous tcgen05/TMA passes (Gram blocks on tcgen05,
+                                      state products as warp-level mma; the default whenever bf16, N = 2,
+                                      D = C in {64, 128}, H a multiple of 4 and no tail_state):
+                                      CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
+
 /* Bytes of workspace cdssm_b200_scan_fused_fwd needs for these sizes (0 on bad sizes). */
 CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C);
 
