@@ -84,6 +84,26 @@ def consts_for(w):
     return (math.log(w["L"]), thr, 16.0 * eps, thr / 5.0, 1.0)
 
 
+def parity_spot_check(w, q, k, v, gate, lds, rope, consts, y, heads=4, tokens=4096):
+    """Untimed: batch row 0, the first `heads` heads and the first `tokens` positions of the benchmarked output
+    against the CPU oracle with the reference's rounding (the scan is causal and heads are independent, so the
+    slice is a complete problem of its own).  Returns max|dy| / max|y_ref|."""
+    import numpy as np
+    import oracle
+    oracle.build()
+    oracle.set_threads(cpu_threads())
+    H, N = w["H"], w["N"]
+    T, hs = min(tokens, q.shape[1]), min(heads, H)
+    f = lambda t: t.float().cpu().numpy()
+    segs = gate.shape[-1] // H
+    g = gate[0:1, :T].reshape(1, T, segs, H)[..., :hs].reshape(1, T, segs * hs)
+    cd = dict(zip(("gating_c", "omega_thresh", "adt_delta", "adt_smoothness", "adt_eps"), consts))
+    ref, _ = oracle.scan_reference(f(q[0:1, :T, :hs]), f(k[0:1, :T, :hs]), f(v[0:1, :T, :hs]), f(g), f(lds[:hs]),
+                                   f(rope[:hs]), cd, N, w["C"], round_bf16=oracle.ROUND_REFERENCE)
+    got = f(y[0:1, :T, :hs])
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons of one GPU, sampled while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -144,6 +164,9 @@ def run_cpu_oracle(w, steps, warmup):
     import numpy as np
     import oracle
     oracle.build()
+    # a launcher may have exported OMP_NUM_THREADS=1: ask for the host threads this process may use and
+    # report the team size the library really got
+    team = oracle.set_threads(cpu_threads())
     s = cpu_sample_workload(w)
     inp = oracle.make_inputs(s["B"], s["H"], s["L"], s["D"], N=s["N"], seed=s["seed"], bf16=True,
                              context_length=w["L"])
@@ -158,7 +181,7 @@ def run_cpu_oracle(w, steps, warmup):
     # tokens/s of the FULL workload's definition (a token = one position across all H heads):
     # the sample has H_s of H heads, so scale token-heads to tokens of the full head count
     tok_heads_per_s = s["B"] * s["L"] * s["H"] / dt
-    return tok_heads_per_s / w["H"], dt, s, float(np.abs(y).max())
+    return tok_heads_per_s / w["H"], dt, s, team
 
 
 def cpu_threads():
@@ -172,8 +195,7 @@ def reference_arm(args, w, rank):
     if rank != 0:
         return
     steps, warmup = max(1, args.steps), max(0, args.warmup)
-    tps, dt, s, _ = run_cpu_oracle(w, steps, warmup)
-    cores = cpu_threads()
+    tps, dt, s, cores = run_cpu_oracle(w, steps, warmup)
     sample = (f"B={s['B']} H={s['H']} L={s['L']} of the workload's B={w['B']} H={w['H']} L={w['L']} "
               f"(same D, N, C); tokens/s = token-heads/s / {w['H']} heads")
     line = {"impl": "reference", "metric": "scan_tokens_per_s", "value": tps, "unit": "tokens/s",
@@ -313,7 +335,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--segments", type=int, default=0, help="cfg4: segments per sequence over all GPUs (default: the workload's)")
-    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (2 = the single-pass tcgen05/TMA kernel, 64 = the four-chain tcgen05/TMA passes)")
+    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (1 = the CUDA-core kernels instead of the tensor-core passes)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -367,11 +389,12 @@ def main():
     consts = consts_for(w)
     y = torch.empty(Bl, Ll, H, N, dtype=dt, device=dev)
     # the library takes its tcgen05/TMA passes by itself for these shapes unless another path is asked for
-    uses_tc4 = bool(args.flags & 64) or (not (args.flags & (1 | 2 | 32)) and N == 2 and D == 128 and C == 128 and H % 4 == 0)
+    tc_shapes = N == 2 and D == C and D in (64, 128) and H % 4 == 0
+    uses_wa = bool(args.flags & 128) or (not (args.flags & (1 | 32)) and tc_shapes)
 
     def step():
         if seq_par:
-            return ops.scan_fused_long(q, k, v, gate, lds, rope, *consts, H, N, C, segments=nseg, flags=args.flags)
+            return ops.scan_fused_long(q, k, v, gate, lds, rope, *consts, H, N, C, segments=nseg, sequence_parallel=world > 1, flags=args.flags)
         return ops.scan_fused(q, k, v, gate, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
 
     def sync_all():
@@ -417,7 +440,7 @@ def main():
                 dg.copy_(hg, non_blocking=True)
                 if seq_par:
                     out, _ = ops.scan_fused_long(dq, dk, dv, dg, lds, rope, *consts, H, N, C,
-                                                 segments=nseg, flags=args.flags)
+                                                 segments=nseg, sequence_parallel=world > 1, flags=args.flags)
                 else:
                     out, _ = ops.scan_fused(dq, dk, dv, dg, lds, rope, *consts, H, N, C, flags=args.flags, out=y)
                 hy.copy_(out, non_blocking=True)
@@ -434,25 +457,30 @@ def main():
         if seq_par:
             tm = {}
             ops.scan_fused_long(q, k, v, gate, lds, rope, *consts, H, N, C,
-                                segments=nseg, flags=args.flags, timings=tm)
+                                segments=nseg, sequence_parallel=world > 1, flags=args.flags, timings=tm)
             t3 = torch.tensor([tm["summary_ms"], tm["handoff_ms"], tm["scan_ms"]], device=dev)
             if dist is not None:
                 dist.all_reduce(t3, op=dist.ReduceOp.MAX)
             extra["segment_passes_ms"] = {"summary": float(t3[0]), "exposed_handoff": float(t3[1]), "scan": float(t3[2])}
-        elif uses_tc4:
+        elif uses_wa:
             # the dominant kernel: the output pass, timed as a call that reuses the local results already in the
             # workspace (records pre-pass + carry pass + output pass; the first two are a few percent of it)
             def output_step():
-                return ops.scan_fused(q, k, v, gate, lds, rope, *consts, H, N, C, flags=64 | ops.REUSE_LOCAL, out=y)
+                return ops.scan_fused(q, k, v, gate, lds, rope, *consts, H, N, C, flags=args.flags | ops.REUSE_LOCAL, out=y)
             output_step()
-            extra["tc4_output_ms"] = timed(output_step, args.steps) / args.steps
-        elif not (args.flags & 2):
+            extra["output_call_ms"] = timed(output_step, args.steps) / args.steps
+        else:
             # the dominant kernel alone: the output pass = whole step minus (local pass + carry pass)
             def summary_step():
                 return ops.scan_summary(k, v, gate, lds, rope, *consts, H, N, C)
             summary_step()
             extra["summary_ms"] = timed(summary_step, args.steps) / args.steps
         t_end = time.time()
+        parity_err = None
+        if rank == 0 and not seq_par:
+            step()
+            torch.cuda.synchronize()
+            parity_err = parity_spot_check(w, q, k, v, gate, lds, rope, consts, y)
     ms_step = ms_total / args.steps
     tokens = w["B"] * L
     scaling = "strong"
@@ -465,24 +493,33 @@ def main():
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic", "config": workload_config(args.workload, w),
                 "clocks": clocks.summary(t_begin, t_end), "e2e": e2e,
-                "gpu_launches": (1 if args.flags & 2 else 4 if uses_tc4 else 3) * args.steps,
+                "gpu_launches": (4 if uses_wa else 3) * args.steps,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                             "kernel": ("scan_tc_kernel (single pass)" if args.flags & 2 else
-                                        "the whole step (tc4_dynamics + scan_tc4 local pass + scan_carry + scan_tc4_out3 "
-                                        "output pass)" if uses_tc4 else
+                             "kernel": ("the whole step (wa_dynamics + scan_wa local pass + scan_carry + scan_wa output "
+                                        "pass)" if uses_wa else
                                         "the whole step (scan_walk local pass + scan_carry + scan_walk output pass)"),
                              "algorithmic_bytes_per_launch": abytes}}
-        if "tc4_output_ms" in extra:
-            out_ms = extra["tc4_output_ms"]
+        if "output_call_ms" in extra:
+            out_ms = extra["output_call_ms"]
             line["roofline"]["dominant_kernel"] = {
-                "name": "tc4::scan_tc4_out3_kernel (output pass)", "ms": out_ms,
+                "name": "wa::scan_wa_kernel<D, true> (output pass)",
+                "ms": out_ms,
                 "achieved": abytes / (out_ms / 1e3) / 1e9, "frac": abytes / (out_ms / 1e3) / 1e9 / peak,
                 "how": "a call that reuses the local pass in the workspace (records pre-pass + carry pass + output "
                        "pass), CUDA-event timed; algorithmic bytes of the whole step"}
-            line["roofline"]["traffic"] = 1.60 * abytes
-            line["roofline"]["traffic_how"] = ("dram bytes read+written per step from an ncu capture of cfg2_L4096 "
-                                               "(profiles/scan_tc4_cfg2_L4096.md), scaled by tokens")
+            # Streams of the four launches per token-head (bf16): pre-pass reads gates + v and writes a 16-byte
+            # record; local pass reads k + record; output pass reads q, k + record and writes y.  The records are
+            # re-read from HBM once they no longer fit the 126 MB L2 (they do at cfg2 L=4096: 33 MB).
+            th = w["B"] * L * H / world
+            rec_bytes = 16 * th
+            rec_reads = 2 * rec_bytes if rec_bytes > 100e6 else 0.0
+            streams = ((N + 5) + N) * 2 * th + rec_bytes + D * 2 * th + 2 * D * 2 * th + N * 2 * th + rec_reads
+            line["roofline"]["traffic"] = streams
+            line["roofline"]["traffic_how"] = ("sum of the kernels' HBM streams (gates, v, 16-byte records written once and "
+                                               "read twice unless they fit L2, k twice, q once, y); agrees with the ncu "
+                                               "dram byte counts of the same kernels at cfg2 L=4096 and L=16384 to a few "
+                                               "percent")
         if "summary_ms" in extra:
             out_ms = ms_step - extra["summary_ms"]
             line["roofline"]["dominant_kernel"] = {
@@ -490,16 +527,22 @@ def main():
                 "achieved": abytes / (out_ms / 1e3) / 1e9, "frac": abytes / (out_ms / 1e3) / 1e9 / peak,
                 "how": "step time minus the time of local pass + carry pass (scan_summary), both CUDA-event timed"}
             line["roofline"]["traffic"] = 1.55 * abytes
-            line["roofline"]["traffic_how"] = ("dram bytes read+written per step from an ncu capture of cfg2_L4096 "
-                                               "(profiles/scan_walk_simt_cfg2_L4096.md), scaled by tokens")
+            line["roofline"]["traffic_how"] = ("dram bytes read+written per step from an ncu capture of the CUDA-core "
+                                               "kernels at cfg2 L=4096, scaled by tokens")
         if "segment_passes_ms" in extra:
             line["segment_passes_ms"] = extra["segment_passes_ms"]
+        if parity_err is not None:
+            line["parity_err"] = parity_err
+            line["parity_how"] = ("batch row 0, heads 0-3, first 4096 tokens of the benchmarked y against the CPU oracle "
+                                  "with the reference's bf16 rounding; max|dy| / max|y|, bound 2e-2")
         if not args.no_cpu_baseline and world == 1:
-            tps, dt_s, s, _ = run_cpu_oracle(w, 5, 1)
-            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+            tps, dt_s, s, team = run_cpu_oracle(w, 5, 1)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": team, "kind": "port",
                                     "sample": f"B={s['B']} H={s['H']} L={s['L']} slice, {dt_s * 1e3:.0f} ms per pass; "
                                               "C restatement of the reference kernels (the reference has no CPU path)"}
         print(json.dumps(line))
+        if parity_err is not None and not parity_err <= 2e-2:
+            raise SystemExit(f"parity spot check failed: {parity_err:.4g} > 2e-2")
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -11,8 +11,8 @@
 //   local pass  : per (chunk, head, pair) walk z only -> gamma_c and z_{C-1}  (workspace)
 //   carry pass  : per (batch, head, pair, d) serial over chunks -> s_c in place of z_{C-1}
 //   output pass : per (chunk, head, pair) walk z and r together, read out y
-// The local pass re-reads k, v and the gates (about half of the algorithmic bytes); the
-// tensor-core kernel in scan_tc.cu is the single-pass version for the shapes it supports.
+// The local pass re-reads k, v and the gates (about half of the algorithmic bytes).  scan_wa.cu holds the
+// tensor-core local and output pass for the shapes it supports; the carry pass here serves both.
 //
 // Thread mapping: eight lanes own one (chunk, head, pair) unit, each lane D/8 contiguous
 // columns of the two state rows, so a k/q row is fetched with 16-byte loads and a dot product
@@ -20,6 +20,7 @@
 // wherever H*N/2 allows, which makes the strided gate and v reads of a block contiguous.
 // The dynamics of a chunk are computed once per unit into shared memory before the walk.
 #include "cdssm_common.cuh"
+#include <atomic>
 
 namespace cdssm {
 
@@ -726,19 +727,8 @@ static int launch_decode(const DecodeArgs& a, cudaStream_t st) {
 
 using namespace cdssm;
 
-namespace cdssm {   // scan_tc.cu
-bool scan_tc_supported(int D, int N, int C, int dtype);
-int scan_fused_tc(const void* q, const void* k, const void* v, const void* gate_raw, const float* log_dt_scale,
-                  const float* rope_freqs, const float* h0, void* y, float* final_state, int* status,
-                  const DynConsts& dc, float shortcut_scale, int B, int L, int H, int pos0, int segs,
-                  cudaStream_t st);
-// scan_tc4.cu
-bool scan_tc4_supported(int D, int N, int C, int H, int dtype);
-size_t scan_tc4_record_bytes(int B, int L, int H);
-int scan_tc4_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
-                      void* rec, const DynConsts& dc, int B, int L, int H, int pos0, int segs, cudaStream_t st);
-int scan_tc4_pass(bool output, bool two_blocks, const void* q, const void* k, const void* rec, float* ws_gamma,
-                  float* ws_state, void* y, int* status, float shortcut_scale, int B, int L, int H, cudaStream_t st);
+namespace cdssm {
+unsigned long long wait_limit_ns();   // c_abi.cu
 // scan_wa.cu
 bool scan_wa_supported(int D, int N, int C, int H, int dtype);
 size_t scan_wa_record_bytes(int B, int L, int H, int C);
@@ -790,14 +780,6 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return CDSSM_ERR_WORKSPACE;
     // first 256 bytes of the workspace: status word of the tensor-core kernel's bounded waits
     int* status = static_cast<int*>(workspace);
-    // The tensor-core kernel is selected explicitly: as measured on B200 it is still slower than
-    // the CUDA-core kernels at the benchmark sizes (one sequential chain per CTA leaves the SM idle).
-    if ((flags & CDSSM_SCAN_TENSOR_CORE) && !(flags & CDSSM_SCAN_FORCE_SIMT) && !summary_only) {
-        if (tail_state != nullptr || !scan_tc_supported(D, N, C, dtype)) return CDSSM_ERR_UNSUPPORTED;
-        return scan_fused_tc(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state, status,
-                             DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps},
-                             shortcut_scale, B, L, H, pos0, segs, (cudaStream_t)stream);
-    }
     if (int rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(int), (cudaStream_t)stream))) return rc;
     workspace = static_cast<char*>(workspace) + 256;
     if ((flags & CDSSM_SCAN_EXACT) && (summary_only || segs != 1)) return CDSSM_ERR_UNSUPPORTED;
@@ -835,47 +817,34 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     // them: measured faster than the CUDA-core walks at every size tried on B200 (2.7x at 64 chunk-head-groups,
     // 1.2x at 4096), so they are taken whenever the shapes allow and nothing else was asked for.  (Bits 256 /
     // 512 keep the CUDA-core local / output pass: used by the tests to check each tensor-core pass alone.)
-    // Warp-autonomous tensor-core passes (scan_wa.cu): the default wherever the shapes allow.
-    const bool wa_ok = tail_state == nullptr && scan_wa_supported(D, N, C, H, dtype);
+    // Warp-autonomous tensor-core passes (scan_wa.cu) for the local and the output pass, with the CUDA-core
+    // carry pass between them: the default wherever the shapes allow.  (Bits 256 / 512 keep the CUDA-core
+    // local / output pass: used by the tests to check each tensor-core pass alone.)
+    // (the tensor-core passes read v and write y as 4-byte pairs: buffers that are only 2-byte aligned, which
+    // the contract allows, stay on the CUDA-core kernels)
+    const bool pair_aligned = ((((uintptr_t)v) | ((uintptr_t)y)) & 3) == 0;
+    const bool wa_ok = tail_state == nullptr && pair_aligned && scan_wa_supported(D, N, C, H, dtype);
     const bool wa_asked = (flags & CDSSM_SCAN_TENSOR_CORE_WA) != 0;
-    if (!(flags & (CDSSM_SCAN_FORCE_SIMT | CDSSM_SCAN_TENSOR_CORE4)) && (wa_asked || wa_ok)) {
+    if (!(flags & CDSSM_SCAN_FORCE_SIMT) && (wa_asked || wa_ok)) {
         if (!wa_ok) return CDSSM_ERR_UNSUPPORTED;
         cudaStream_t st = (cudaStream_t)stream;
         const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
+        const int withhold = (flags & CDSSM_SCAN_TEST_WITHHOLD) ? 1 : 0;
+        const unsigned long long limit = wait_limit_ns();
         void* rec = reinterpret_cast<char*>(a.ws_state) + align256((size_t)a.units * 2 * D * sizeof(float));
         if (int rc = scan_wa_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, C, pos0, segs, st))
             return rc;
         if (a.run_local && tc_local) {
             if (int rc = scan_wa_pass(false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale, B, L, H,
-                                      D, 0, 0, st))
+                                      D, limit, withhold, st))
                 return rc;
             a.run_local = 0;
         }
         a.run_output = tc_output ? 0 : 1;
         if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;   // carry pass (+ whatever was kept)
         if (!tc_output || summary_only) return CDSSM_OK;
-        return scan_wa_pass(true, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L, H, D, 0, 0, st);
-    }
-    const bool tc4_ok = tail_state == nullptr && scan_tc4_supported(D, N, C, H, dtype);
-    const bool tc4_asked = (flags & CDSSM_SCAN_TENSOR_CORE4) != 0;
-    if (!(flags & CDSSM_SCAN_FORCE_SIMT) && (tc4_asked || tc4_ok)) {
-        if (!tc4_ok) return CDSSM_ERR_UNSUPPORTED;
-        cudaStream_t st = (cudaStream_t)stream;
-        const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
-        void* rec = reinterpret_cast<char*>(a.ws_state) + align256((size_t)a.units * 2 * D * sizeof(float));
-        if (int rc = scan_tc4_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, pos0, segs, st))
-            return rc;
-        if (a.run_local && tc_local) {
-            if (int rc = scan_tc4_pass(false, false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale,
-                                       B, L, H, st))
-                return rc;
-            a.run_local = 0;
-        }
-        a.run_output = tc_output ? 0 : 1;
-        if (int rc = scan_fused_simt(a, dtype, false, st)) return rc;   // carry pass (+ whatever was kept)
-        if (!tc_output || summary_only) return CDSSM_OK;
-        return scan_tc4_pass(true, (flags & 1024) != 0, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L,
-                             H, st);   // bit 1024: the output pass with three tile buffers, two blocks per SM
+        return scan_wa_pass(true, q, k, rec, a.ws_gamma, a.ws_state, y, status, shortcut_scale, B, L, H, D, limit,
+                            withhold, st);
     }
     return scan_fused_simt(a, dtype, false, (cudaStream_t)stream);
 }
@@ -967,6 +936,8 @@ extern "C" int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const v
 // is this address that the kernels receive.
 constexpr size_t kNoAllocScratchBytes = 16u << 20;   // 16 MiB
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+constexpr int kNoAllocMaxDevices = 64;
+static std::atomic<void*> g_noalloc_scratch_of_device[kNoAllocMaxDevices];   // device address of the array, per device
 
 extern "C" size_t cdssm_b200_scan_fused_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
 
@@ -978,8 +949,6 @@ extern "C" int cdssm_b200_scan_fused_fwd_noalloc(const void* q, const void* k, c
                                                  float adt_smoothness, float adt_eps,
                                                  float shortcut_scale, int B, int L, int H, int D, int N,
                                                  int C, int pos0, int dtype, int flags, void* stream) {
-    constexpr int kMaxDevices = 64;
-    static void* scratch_of_device[kMaxDevices] = {nullptr};
     if (B <= 0 || L <= 0) {   // nothing to do, but still validate like the allocating entry point
         return cdssm_b200_scan_fused_fwd(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state,
                                          tail_state, nullptr, 0, gating_c, omega_thresh, adt_delta,
@@ -991,19 +960,30 @@ extern "C" int cdssm_b200_scan_fused_fwd_noalloc(const void* q, const void* k, c
     if (need > kNoAllocScratchBytes) return CDSSM_ERR_WORKSPACE;   // beyond the built-in scratch
     int dev = 0;
     if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
-    if (dev < 0 || dev >= kMaxDevices) return CDSSM_ERR_UNSUPPORTED;
-    if (scratch_of_device[dev] == nullptr) {
-        // one-time set-up for this device (do it before any stream capture begins)
-        void* p = nullptr;
-        if (int rc = check_cuda(cudaGetSymbolAddress(&p, g_noalloc_scratch))) return rc;
-        scratch_of_device[dev] = p;
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return CDSSM_ERR_UNSUPPORTED;
+    void* scratch = g_noalloc_scratch_of_device[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
+        // one-time set-up for this device (do it before any stream capture begins); two host threads that
+        // race here both look up the same address
+        if (int rc = check_cuda(cudaGetSymbolAddress(&scratch, g_noalloc_scratch))) return rc;
+        g_noalloc_scratch_of_device[dev].store(scratch, std::memory_order_release);
     }
     // Nothing in the scratch has to start at zero except the status word, which the scan itself
     // clears on the stream; gamma/state slots are all written by the local pass before they are read.
     return cdssm_b200_scan_fused_fwd(q, k, v, gate_raw, log_dt_scale, rope_freqs, h0, y, final_state,
-                                     tail_state, scratch_of_device[dev], kNoAllocScratchBytes, gating_c,
+                                     tail_state, scratch, kNoAllocScratchBytes, gating_c,
                                      omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, L,
                                      H, D, N, C, pos0, dtype, flags, stream);
+}
+
+extern "C" int cdssm_b200_scan_fused_noalloc_status(int* status_host, void* stream) {
+    if (!status_host) return CDSSM_ERR_BAD_ARG;
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return CDSSM_ERR_UNSUPPORTED;
+    void* p = g_noalloc_scratch_of_device[dev].load(std::memory_order_acquire);
+    if (!p) return CDSSM_ERR_BAD_ARG;   // no allocation-free call has run on this device yet
+    return cdssm_b200_scan_fused_status(p, status_host, stream);
 }
 
 extern "C" int cdssm_b200_decode_step(float* state, const void* q, const void* k, const void* v,

@@ -21,7 +21,7 @@ from ._lib import CdssmError, check
 
 __all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
            "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
-           "scan_fused_workspace_bytes", "scan_fused_status", "scan_summary", "scan_fused_long", "compose_carries",
+           "scan_fused_workspace_bytes", "scan_fused_status", "set_wait_limit_ns", "selftest_bounded_wait", "scan_summary", "scan_fused_long", "compose_carries",
            "CdssmError"]
 
 _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
@@ -196,11 +196,10 @@ class ExactCorrectionFn(Function):
 # Level 2: the fused path
 # ------------------------------------------------------------------------------------------
 FORCE_SIMT = 1
-TENSOR_CORE = 2
 REUSE_LOCAL = 8
 EXACT = 32
-TENSOR_CORE4 = 64
 TENSOR_CORE_WA = 128
+TEST_WITHHOLD = 2048   # self-test of the bounded waits: see include/cdssm_b200.h
 
 _workspaces = {}
 
@@ -225,7 +224,7 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
                adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int,
                chunk_size: int, h0: Tensor = None, *, shortcut_scale: float = 0.0, pos0: int = 0,
                return_tail_state: bool = False, flags: int = 0, out: Tensor = None, segs: int = 1,
-               semantics: str = "reference"):
+               semantics: str = "reference", strict: bool = False):
     """The scan path of one CD-SSM block in a single call.
 
     Equals, in the reference (cdssm/models/block.py:181-211): DynamicsFusedFn -> NormalizeKQFn
@@ -242,6 +241,9 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
     tail_state is the recurrent state after the last token (what decode_step continues from).
     semantics="exact" runs the plain sequential recurrence instead of the reference's chunk semantics
     (identical inside the first chunk); h0/final_state are then the recurrent state.
+    strict=True synchronises the stream after the call and raises if a bounded device-side wait of the
+    tensor-core kernels ran out (the outputs are undefined then); without it the call stays asynchronous
+    and :func:`scan_fused_status` reports the same word on demand.
     """
     if semantics not in ("reference", "exact"):
         raise CdssmError("semantics must be 'reference' (the reference's chunked scan, bug for bug) or "
@@ -287,6 +289,10 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
                 _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(y), _p(final), ws_ptr, ws_bytes,
                 gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, L, H, D, N,
                 C, int(pos0), int(segs), _dtype_code(q), int(flags), _stream()), "scan_fused_segmented_fwd")
+    if strict:
+        code = scan_fused_status(dev)
+        if code != 0:
+            raise CdssmError(f"scan_fused: a device-side wait ran out (status {code}); the outputs are undefined")
     return (y, final, tail) if return_tail_state else (y, final)
 
 
@@ -350,6 +356,22 @@ def scan_fused_status(device=None) -> int:
     return out.value
 
 
+def set_wait_limit_ns(limit_ns: int) -> int:
+    """Limit of the bounded device-side waits of the tensor-core kernels (0 = the 400 ms default).
+    Returns the previous limit."""
+    return int(_lib.lib().cdssm_b200_set_wait_limit_ns(int(limit_ns)))
+
+
+def selftest_bounded_wait(limit_ns: int = 1_000_000, device=None) -> int:
+    """Runs the wait primitive of the tensor-core kernels on a barrier that nothing signals.
+    Returns 1 if the wait gave up after ``limit_ns`` as it must, 2 if it claimed to be signalled."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = torch.zeros(1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        check(_lib.lib().cdssm_b200_selftest_bounded_wait(_p(st), int(limit_ns), _stream()), "selftest_bounded_wait")
+    return int(st.item())
+
+
 def scan_summary(k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor, rope_freqs: Tensor,
                  gating_c: float, omega_thresh: float, adt_delta: float, adt_smoothness: float,
                  adt_eps: float, n_heads: int, state_dim: int, chunk_size: int, h0: Tensor = None, *,
@@ -382,11 +404,14 @@ def scan_summary(k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor, r
 def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor,
                     rope_freqs: Tensor, gating_c: float, omega_thresh: float, adt_delta: float,
                     adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int, chunk_size: int,
-                    h0: Tensor = None, *, segments: int = 1, group=None, shortcut_scale: float = 0.0,
-                    pos0: int = 0, flags: int = 0, timings: dict = None):
-    """The fused scan of long sequences cut into chunk-aligned segments, on one GPU or one
-    contiguous piece per rank of ``group`` (torch.distributed; rank r holds tokens
-    [r*L, (r+1)*L) of every sequence).
+                    h0: Tensor = None, *, segments: int = 1, sequence_parallel: bool = False, group=None,
+                    shortcut_scale: float = 0.0, pos0: int = 0, flags: int = 0, timings: dict = None):
+    """The fused scan of long sequences cut into chunk-aligned segments, on one GPU or - only with
+    ``sequence_parallel=True`` (or an explicit ``group``) - one contiguous piece per rank of a
+    torch.distributed group (rank r holds tokens [r*L, (r+1)*L) of every sequence; ``group=None`` is then
+    the default group).  Without either, an initialised process group is ignored: in a data-parallel job
+    every rank scans its own sequences.  ``h0`` is the carry into the FIRST token of the whole sequence;
+    rank 0's value is broadcast to the group.
 
     Pass A summarises every segment (k, v, gates only); the ranks exchange their (decay, carry)
     summaries with one small all-gather; the carries into all segments follow from the serial
@@ -401,9 +426,11 @@ def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_sc
     Ls = L // S
     seg = lambda t: t.contiguous().view(B * S, Ls, *t.shape[2:])
     consts = (gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps)
-    rank, world = 0, 1
-    if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
-        rank, world = torch.distributed.get_rank(group), torch.distributed.get_world_size(group)
+    rank, world = sharding.sequence_ranks(sequence_parallel, group)
+    if world > 1 and h0 is not None:
+        h0 = _prep(h0, dtype=torch.float32, name="h0").clone()
+        torch.distributed.broadcast(h0, torch.distributed.get_global_rank(group, 0) if group is not None else 0,
+                                    group=group)
     base = pos0 + rank * L
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
     if ev: ev[0].record()
@@ -422,7 +449,7 @@ def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_sc
     if ev: ev[2].record()
     y, _ = scan_fused(seg(q), seg(k), seg(v), seg(gate_raw), log_dt_scale, rope_freqs, *consts, n_heads, N, C,
                       h_rows, shortcut_scale=shortcut_scale, pos0=base, segs=S,
-                      flags=flags if flags & TENSOR_CORE else flags | REUSE_LOCAL)   # pass A's local results
+                      flags=flags | REUSE_LOCAL)   # pass A's local results
     if ev:
         ev[3].record()
         torch.cuda.synchronize()

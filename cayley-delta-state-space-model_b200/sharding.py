@@ -71,6 +71,19 @@ def compose_carries(decay: torch.Tensor, carry_out: torch.Tensor, h0: torch.Tens
     return torch.stack(ins), s
 
 
+def sequence_ranks(sequence_parallel: bool = False, group=None):
+    """(rank, world) of the sequence-parallel scan.  Sequence parallelism is opt-in: it is taken only when
+    asked for (``sequence_parallel=True``) or when a process group is passed explicitly.  A process group
+    that merely happens to be initialised - the usual state of a data-parallel job, where every rank scans
+    its own sequences - means a single piece: (0, 1)."""
+    if not sequence_parallel and group is None:
+        return 0, 1
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        raise RuntimeError("sequence_parallel needs an initialised torch.distributed process group")
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
 def exchange_summaries(decay: torch.Tensor, carry_out: torch.Tensor, group=None):
     """All-gather the (Gamma, b) summaries of every rank's segment.  decay (B,H,N), carry_out
     (B,H,N,D) of the local segment -> (world, B,H,N), (world, B,H,N,D).  One small collective;

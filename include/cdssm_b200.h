@@ -99,17 +99,15 @@ CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, cons
                                       over the whole sequence (what the reference equals inside its first
                                       chunk and what decode continues); h0/final_state/tail_state are then
                                       the recurrent state.  One sequential walk per (batch, head, pair). */
-#define CDSSM_SCAN_TENSOR_CORE 2   /* use the single-pass tcgen05/TMA kernel: bf16, N = 2, D = C = 128,
-                                      no tail_state; CDSSM_ERR_UNSUPPORTED for other sizes */
-#define CDSSM_SCAN_TENSOR_CORE4 64 /* insist on the tcgen05/TMA passes that walk four heads' chunks per thread block
-                                      in 32-token sub-blocks (local and output pass; the default whenever bf16,
-                                      N = 2, D = C = 128, H a multiple of 4 and no tail_state):
-                                      CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
-
 #define CDSSM_SCAN_TENSOR_CORE_WA 128 /* insist on the warp-autonomous tcgen05/TMA passes (Gram blocks on tcgen05,
                                       state products as warp-level mma; the default whenever bf16, N = 2,
                                       D = C in {64, 128}, H a multiple of 4 and no tail_state):
                                       CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
+
+#define CDSSM_SCAN_TEST_WITHHOLD 2048 /* self-test of the bounded device-side waits (tensor-core passes only): the
+                                      producer warp issues no load and no UMMA, so the first wait of every
+                                      compute warp runs out after the wait limit, the kernels unwind and set
+                                      the status word; outputs are undefined.  Never faults or hangs. */
 
 /* Bytes of workspace cdssm_b200_scan_fused_fwd needs for these sizes (0 on bad sizes). */
 CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int D, int N, int C);
@@ -119,8 +117,8 @@ CDSSM_API size_t cdssm_b200_scan_fused_workspace_bytes(int B, int L, int H, int 
  * chunk semantics (local scan from zero per chunk of C tokens, decay-only carry between chunks,
  * correction taken before each step) -> shortcut -> read-out with q -> sel_C gate.
  * Supported: even N <= 32, D <= 128, C <= 256, bf16 or fp32 (CUDA-core kernels, three launches);
- * bf16 with N = 2, D = C = 128, H a multiple of 4 and no tail_state runs on the tensor cores (tcgen05/TMA
- * local and output pass, four launches); with CDSSM_SCAN_TENSOR_CORE: the older single-pass tcgen05/TMA kernel.
+ * bf16 with N = 2, D = C in {64, 128}, H a multiple of 4 and no tail_state runs on the tensor cores (tcgen05/TMA
+ * local and output pass, four launches).
  *   q,k (B,L,H,D) un-normalised; v (B,L,H,N) before the vp scale; gate_raw (B,L,(N+5)*H);
  *   h0 (B,H,N,D) float32 or NULL: carry into the first chunk;
  *   y (B,L,H,N); final_state (B,H,N,D) float32 or NULL: carry after the last chunk;
@@ -214,6 +212,22 @@ CDSSM_API size_t cdssm_b200_scan_fused_noalloc_max_bytes(void);
  * CDSSM_ERR_TIMEOUT (the outputs of that call are then undefined; the context stays usable).
  * No reference counterpart: the reference has no device-side waits. */
 CDSSM_API int cdssm_b200_scan_fused_status(const void* workspace, int* status_host, void* stream);
+
+/* cdssm_b200_scan_fused_status for the allocation-free entry point: reads the status word that the last
+ * cdssm_b200_scan_fused_fwd_noalloc call on the current device left in the built-in scratch
+ * (synchronises `stream`).  CDSSM_ERR_BAD_ARG if no such call has been made on this device.
+ * No reference counterpart. */
+CDSSM_API int cdssm_b200_scan_fused_noalloc_status(int* status_host, void* stream);
+
+/* Limit of every bounded device-side wait of the tensor-core kernels, in nanoseconds of the GPU's global
+ * timer (process-wide; default and 0 = 400 ms).  A wait that runs out makes its kernel unwind and set the
+ * status word instead of hanging.  Returns the previous limit.  No reference counterpart. */
+CDSSM_API uint64_t cdssm_b200_set_wait_limit_ns(uint64_t limit_ns);
+
+/* Self-test of the bounded wait primitive: one thread block waits on a barrier that nothing signals, for at
+ * most limit_ns, then writes 1 (the wait gave up, as it must) or 2 (it returned as if signalled) to
+ * *status_dev and returns.  No reference counterpart. */
+CDSSM_API int cdssm_b200_selftest_bounded_wait(int* status_dev, uint64_t limit_ns, void* stream);
 
 /* One-token recurrent decode step for a batch of sequences: dynamics for position `pos`,
  * normalise q/k, state <- a (*) (state - beta (state k) k^T) + beta v k^T, y = sel_C * (state q

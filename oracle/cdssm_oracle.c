@@ -406,3 +406,22 @@ done:
     free(A); free(vp); free(be); free(sc); free(kn); free(qn);
     return rc;
 }
+
+/* Size of the OpenMP team (test and benchmark infrastructure).  A launcher such as torch.distributed.run
+ * exports OMP_NUM_THREADS=1 to its children; the CPU baseline asks for the host threads it may really use
+ * and reports the team size it got.  Without OpenMP both return 1. */
+#ifdef _OPENMP
+#include <omp.h>
+int orc_set_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+    int got = 1;
+#pragma omp parallel
+    {
+#pragma omp single
+        got = omp_get_num_threads();
+    }
+    return got;
+}
+#else
+int orc_set_threads(int n) { (void)n; return 1; }
+#endif

@@ -16,7 +16,7 @@ _LIB = None
 
 __all__ = ["build", "lib", "bf16_round", "derive_constants", "dynamics", "normalize_kq",
            "intra_chunk", "inter_chunk", "exact_correction", "conv1d_silu", "scan_reference",
-           "scan_recurrent", "make_inputs", "rope_freqs_default", "ROUND_NONE", "ROUND_INPUTS", "ROUND_STATE",
+           "scan_recurrent", "make_inputs", "set_threads", "rope_freqs_default", "ROUND_NONE", "ROUND_INPUTS", "ROUND_STATE",
            "ROUND_CARRY", "ROUND_OUTPUTS", "ROUND_REFERENCE", "ROUND_FP32_STATE"]
 
 
@@ -58,6 +58,14 @@ def _mask(round_bf16):
     if round_bf16 is False or round_bf16 is None:
         return 0
     return int(round_bf16)
+
+
+def set_threads(n):
+    """Ask for an OpenMP team of n threads; returns the team size the library really runs with."""
+    fn = lib().orc_set_threads
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int]
+    return int(fn(int(n)))
 
 
 def bf16_round(a):

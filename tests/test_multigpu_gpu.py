@@ -38,7 +38,7 @@ def _worker(rank, world, port, q_out):
     lo, hi = rank * L // world, (rank + 1) * L // world
     seg = [x[:, lo:hi].contiguous() for x in full]
     tm = {}
-    y_s, f_s = ops.scan_fused_long(*seg, lds, rf, *consts, H, N, C, segments=2, timings=tm)
+    y_s, f_s = ops.scan_fused_long(*seg, lds, rf, *consts, H, N, C, segments=2, sequence_parallel=True, timings=tm)
     torch.cuda.synchronize()
     q_out.put((rank, y_b.float().cpu().numpy(), f_b.cpu().numpy(), y_s.float().cpu().numpy(), f_s.cpu().numpy(), tm))
     dist.barrier()

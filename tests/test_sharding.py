@@ -47,6 +47,10 @@ def _worker(rank, world, port, mask, out_q):
     inp = orc.make_inputs(B, H, L, D, N=N, seed=3, bf16=mask != 0)
     lo, hi = sh.segment_bounds(L, C, world)[rank]
     dec, b_seg, sl = _segment_summary(orc, inp, lo, hi, mask)
+    # sequence parallelism is opt-in: an initialised default group alone means "this rank's own sequences"
+    assert sh.sequence_ranks() == (0, 1)
+    assert sh.sequence_ranks(sequence_parallel=True) == (rank, world)
+    assert sh.sequence_ranks(group=dist.group.WORLD) == (rank, world)
     decs, outs = sh.exchange_summaries(torch.from_numpy(dec), torch.from_numpy(b_seg))
     carry_in, final = sh.compose_carries(decs, outs)
     y, fin = orc.scan_reference(sl["q"], sl["k"], sl["v"], sl["gate_raw"], sl["log_dt_scale"], sl["rope_freqs"],
@@ -110,3 +114,10 @@ def test_compose_carries_is_the_serial_recurrence():
         a = torch.complex(dec[k][..., 0::2], dec[k][..., 1::2])[..., None]
         s = a * s + torch.complex(out[k][..., 0::2, :], out[k][..., 1::2, :])
     assert torch.allclose(torch.complex(fin[..., 0::2, :], fin[..., 1::2, :]), s, atol=1e-6)
+
+
+def test_sequence_ranks_without_a_process_group():
+    import cdssm_b200.sharding as sh
+    assert sh.sequence_ranks() == (0, 1)
+    with pytest.raises(RuntimeError):
+        sh.sequence_ranks(sequence_parallel=True)

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 def _call(lib, name, t, consts, dims, extra_ws=None):
     q, k, v, g, lds, rf, h0, y, fin, tail = t
-    args = [x.data_ptr() for x in (q, k, v, g, lds, rf, h0, y, fin, tail)]
+    args = [0 if x is None else x.data_ptr() for x in (q, k, v, g, lds, rf, h0, y, fin, tail)]
     if extra_ws is not None:
         args += [extra_ws.data_ptr() + (-extra_ws.data_ptr()) % 256, extra_ws.numel() - 256]
     args += [ctypes.c_float(c) for c in consts] + [ctypes.c_float(0.25)] + list(dims)
@@ -51,6 +51,35 @@ def test_noalloc_entry_matches_allocating_entry(ops, orc, B, H, L, D, N, C):
             err = float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-30))
             assert err <= 2.0 ** -7, (attempt, name, err)      # same kernels: in practice exactly equal
             assert torch.equal(a, b), (attempt, name)
+
+
+def test_noalloc_entry_on_the_tensor_core_passes_reports_its_status(ops, orc):
+    """A shape that takes the tcgen05 passes (no tail_state): their records and carries live in the built-in
+    scratch, and the status word is read through the entry point made for callers without a workspace."""
+    import cdssm_b200
+    lib = cdssm_b200._lib.lib()
+    B, H, L, D, N, C = 1, 4, 512, 128, 2, 128
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=32, bf16=True)
+    dev = torch.device("cuda", 0)
+    bf = lambda a: torch.from_numpy(a).to(dev).bfloat16().contiguous()
+    f32 = lambda a: torch.from_numpy(a).to(dev).float().contiguous()
+    base = [bf(inp["q"]), bf(inp["k"]), bf(inp["v"]), bf(inp["gate_raw"]), f32(inp["log_dt_scale"]),
+            f32(inp["rope_freqs"]), None]
+    outs = lambda: [torch.full((B, L, H, N), 3.0, device=dev, dtype=torch.bfloat16),
+                    torch.full((B, H, N, D), 3.0, device=dev), None]
+    consts, dims = const_args(inp["consts"]), (B, L, H, D, N, C)
+    ws = torch.empty(ops.scan_fused_workspace_bytes(B, L, H, D, N, C) + 512, dtype=torch.uint8, device=dev)
+    ref = outs()
+    assert _call(lib, "cdssm_b200_scan_fused_fwd", base + ref, consts, dims, extra_ws=ws) == 0
+    torch.cuda.synchronize()
+    for attempt in range(2):
+        got = outs()
+        assert _call(lib, "cdssm_b200_scan_fused_fwd_noalloc", base + got, consts, dims) == 0
+        status = ctypes.c_int(-1)
+        assert lib.cdssm_b200_scan_fused_noalloc_status(ctypes.addressof(status),
+                                                        torch.cuda.current_stream().cuda_stream) == 0
+        assert status.value == 0
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), attempt
 
 
 def test_noalloc_entry_refuses_sizes_beyond_its_scratch(ops):
