@@ -104,6 +104,40 @@ def parity_spot_check(w, q, k, v, gate, lds, rope, consts, y, heads=4, tokens=40
     return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
 
 
+def reference_gpu_leg(w, q, k, v, gate, lds, rope, consts, ops, tokens=4096, reps=3):
+    """Context figure, outside the product path: the reference's OWN kernels (compiled unmodified for sm_100
+    into oracle/_ref by oracle/build_ref.py) and its glue, on the first `tokens` positions of the benchmark
+    inputs, CUDA-event timed, beside this library's fused call on the same slice.  None if the extension
+    was not built."""
+    import torch
+    from oracle.build_ref import load_ref
+    from oracle.ref_pipeline import reference_forward
+    ref = load_ref()
+    if ref is None:
+        return None
+    H, N, C = w["H"], w["N"], w["C"]
+    T = min(tokens, q.shape[1])
+    sl = [t[:, :T].contiguous() for t in (q, k, v, gate)]
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ref_ms = timed(lambda: reference_forward(ref, *sl, lds, rope, consts, H, N, C))
+    our_ms = timed(lambda: ops.scan_fused(*sl, lds, rope, *consts, H, N, C))
+    return {"ms": ref_ms, "this_library_ms": our_ms,
+            "workload": f"B={q.shape[0]} H={H} L={T} head_dim={w['D']} (first {T} tokens of the benchmark inputs)",
+            "what": "dynamics_fused + normalize (torch for head_dim 128) + intra_chunk_scan + inter_chunk_scan + "
+                    "exact_correction kernels of the reference recompiled for sm_100, with the reference's torch glue"}
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons of one GPU, sampled while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -531,6 +565,13 @@ def main():
                                                "kernels at cfg2 L=4096, scaled by tokens")
         if "segment_passes_ms" in extra:
             line["segment_passes_ms"] = extra["segment_passes_ms"]
+        if not args.no_cpu_baseline and world == 1 and not seq_par:
+            try:
+                rg = reference_gpu_leg(w, q, k, v, gate, lds, rope, consts, ops)
+            except Exception as e:   # context only: never fail the benchmark line over it
+                rg = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+            if rg is not None:
+                line["reference_gpu"] = rg
         if parity_err is not None:
             line["parity_err"] = parity_err
             line["parity_how"] = ("batch row 0, heads 0-3, first 4096 tokens of the benchmarked y against the CPU oracle "

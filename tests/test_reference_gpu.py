@@ -50,3 +50,22 @@ def test_against_reference_kernels(ops, orc, ref, case):
     # the fused path against the reference pipeline's final output
     y, _ = ops.scan_fused(q, k, v, gate, lds, rf, *consts, H, N, C, shortcut_scale=float(g["shortcut"]))
     assert rel_err(to_np(y), unbits(g["y"])) <= BF16_TOL
+
+
+@pytest.mark.parametrize("B,H,L,D", [(2, 4, 512, 64), (1, 8, 300, 64), (1, 32, 1024, 128), (2, 4, 700, 128)])
+def test_tensor_core_passes_against_reference_kernels(ops, orc, ref, B, H, L, D):
+    """Shapes that take the tcgen05 passes (H a multiple of 4, head_dim 64 and 128), against the live
+    reference pipeline on the same un-normalised bf16 inputs."""
+    from oracle.ref_pipeline import reference_forward
+    N, C = 2, D
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=100 + L + D, bf16=True)
+    bf = lambda a: torch.from_numpy(a).cuda().bfloat16()
+    q, k, v, gate = bf(inp["q"]), bf(inp["k"]), bf(inp["v"]), bf(inp["gate_raw"])
+    scale = torch.linspace(0.5, 3.0, L, device="cuda").view(1, L, 1, 1).bfloat16()
+    q, k = (q * scale).contiguous(), (k * scale.flip(1)).contiguous()
+    lds, rf = torch.from_numpy(inp["log_dt_scale"]).cuda(), torch.from_numpy(inp["rope_freqs"]).cuda()
+    consts = const_args(inp["consts"])
+    want = reference_forward(ref, q, k, v, gate, lds, rf, consts, H, N, C, shortcut=0.5)
+    y, _ = ops.scan_fused(q, k, v, gate, lds, rf, *consts, H, N, C, shortcut_scale=0.5, flags=ops.TENSOR_CORE_WA)
+    assert ops.scan_fused_status() == 0
+    assert rel_err(to_np(y), to_np(want)) <= BF16_TOL
