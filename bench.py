@@ -29,6 +29,8 @@ WORKLOADS = {  # the scan-kernel sweep: bf16 q/k/v, fp32 state, seed 2
                          B=8, L=2048, seed=1, H=24, D=64, N=2, C=64),
     "cfg3_decode": dict(lm=dict(d_model=2048, n_layers=24, vocab_size=32000, state_dim=2, context_length=4608),
                         B=256, L=4096, decode_steps=512, seed=3, H=64, D=64, N=2, C=64),
+    # the one-token decode kernel alone: cfg3's per-layer shapes, graph replay over 24 layers' states
+    "decode_kernel": dict(decode_kernel=True, B=256, H=64, D=64, N=2, layers=24, L=4608, seed=3),
     "cfg4_L1M": dict(B=1, H=32, D=128, N=2, C=128, L=1 << 20, seed=4, seq_parallel=True, segments=16),
 }
 DEFAULT_WORKLOAD = "cfg2_L65536"
@@ -358,6 +360,71 @@ def lm_arm(args, w, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def decode_kernel_arm(args, w, local_rank):
+    """cdssm_b200_decode_step alone at cfg3's per-layer shapes: one CUDA graph holds one launch per layer over 24
+    separate (B,H,N,D) fp32 states (201 MB, more than the L2), replayed; reports microseconds per launch and
+    the fraction of the HBM roofline against the 1302 algorithmic bytes per (batch, head).  `floor` is the same
+    harness around a plain in-place torch kernel over the same states (two thirds of the bytes): what a launch
+    of this size costs with no arithmetic at all."""
+    import torch
+    from cdssm_b200 import ops
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    B, H, D, N, layers = w["B"], w["H"], w["D"], w["N"], w["layers"]
+    g = torch.Generator(device=dev).manual_seed(w["seed"])
+    rn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    q, k = rn(B, H, D).bfloat16(), rn(B, H, D).bfloat16()
+    v, gate = rn(B, H, N).bfloat16(), rn(B, (N + 5) * H).bfloat16()
+    lds = torch.zeros(H, device=dev)
+    rope = (1.0 / (float(w["L"]) ** (torch.arange(H, dtype=torch.float32) / H))).to(dev)
+    consts = consts_for(w)
+    y = torch.empty(B, H, N, device=dev, dtype=torch.bfloat16)
+    states = [rn(B, H, N, D) * 0.1 for _ in range(layers)]
+
+    def replayed(fn, reps):
+        for s in states:
+            fn(s)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for s in states:
+                fn(s)
+        for _ in range(max(3, args.warmup)):
+            gr.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps / layers * 1e3      # microseconds per launch
+
+    reps = max(20, args.steps)
+    with ClockSampler(local_rank) as clocks:
+        t0 = time.time()
+        us = replayed(lambda s: ops.decode_step(s, q, k, v, gate, lds, rope, *consts, H, N, 4096, out=y), reps)
+        floor_us = replayed(lambda s: s.mul_(1.0), reps)
+        t1 = time.time()
+    per_bh = 2 * N * D * 4 + 2 * D * 2 + (3 * N + 5) * 2
+    abytes = B * H * per_bh
+    peak, peak_kind = peaks()
+    achieved = abytes / (us * 1e-6) / 1e9
+    line = {"metric": "decode_kernel_us_per_layer", "value": us, "unit": "us", "n_gpus": 1, "steps": reps,
+            "warmup": max(3, args.warmup), "ms_per_step": us * layers / 1e3, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 state, bf16 activations", "data": "synthetic",
+            "config": {"workload": f"decode_kernel: one-token decode step, B={B} H={H} head_dim={D} state_dim={N}, "
+                                   f"{layers} layers' states ({layers * B * H * N * D * 4 / 1e6:.0f} MB) per graph replay",
+                       "l2": "the states of one replay exceed the 126 MB L2"},
+            "clocks": clocks.summary(t0, t1), "e2e": None, "gpu_launches": reps * layers,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "decode_step_kernel<bf16, 8>",
+                         "algorithmic_bytes_per_launch": abytes},
+            "floor": {"us": floor_us, "bytes": 2 * B * H * N * D * 4,
+                      "what": "in-place torch elementwise kernel over the same states in the same replay harness"}}
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------ the GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -382,6 +449,10 @@ def main():
         args.warmup = 3
     if "lm" in w:
         return lm_arm(args, w, rank, world, local_rank)
+    if w.get("decode_kernel"):
+        if rank == 0:
+            decode_kernel_arm(args, w, local_rank)
+        return
 
     import torch
     import cdssm_b200

@@ -197,7 +197,6 @@ __device__ __forceinline__ void producer(Smem<kD, kOutput>& sm, const CUtensorMa
                 if (n < NS) {
                     if (kOutput) {   // every warp has taken rho and |q| of step g from the Q tile (and P has read it)
                         if (!wait(&sm.q_free, g & 1)) { code = 3; break; }
-                        WA_PSTAMP(n, 12);
                         load_tile(sm.q, tmQ, &sm.full_q, n); pend_q = n & 1;
                     }
                     // every warp has G and P of step g in registers
@@ -420,12 +419,15 @@ __device__ __forceinline__ float pick32(const float (&x)[32], int idx) {
     return (idx & 16) ? d1 : d0;
 }
 
-// bf16 pair for an mma operand: the high parts of (x0, x1) if !low, else the parts that the high parts left over
+// bf16 pair for an mma operand from two fp32 values split as x = hi + lo with hi = x truncated to bf16 (exact
+// in fp32, so lo = x - hi is exact too) and lo truncated to bf16 in turn: hi + lo carries 16 significant bits.
+// low = false gives the pair of high parts, low = true the pair of low parts.  Truncation keeps the whole split
+// on the integer and FMA pipes (mask, subtract, byte permute) - no conversion instructions.
 __device__ __forceinline__ uint32_t split_pack(float x0, float x1, bool low) {
-    const uint32_t hi = pack2(x0, x1);
-    const uint32_t m = low ? 0xffffffffu : 0u;
-    const float r0 = x0 - __uint_as_float((hi << 16) & m), r1 = x1 - __uint_as_float(hi & 0xffff0000u & m);
-    return pack2(r0, r1);
+    const uint32_t m = low ? 0xffff0000u : 0u;
+    const float r0 = x0 - __uint_as_float(__float_as_uint(x0) & m);
+    const float r1 = x1 - __uint_as_float(__float_as_uint(x1) & m);
+    return __byte_perm(__float_as_uint(r0), __float_as_uint(r1), 0x7632);   // {r1[31:16], r0[31:16]}
 }
 
 template <int kD, bool kOutput>
@@ -515,6 +517,7 @@ __device__ __forceinline__ void compute(Smem<kD, kOutput>& sm, const Args& a) {
             bfrag[ks][0] = split_pack(S[ks][0], S[ks][1], low);
             bfrag[ks][1] = split_pack(S[ks][2], S[ks][3], low);
         }
+        WA_STAMP(12);
         float ak[2][4], aq[2][4], qa[2][4], qb[2][4];
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
@@ -698,9 +701,9 @@ __device__ __forceinline__ void compute(Smem<kD, kOutput>& sm, const Args& a) {
                     x0 = *reinterpret_cast<const float2*>(om + np * 32 + 16 * kk + 2 * tig);
                     x1 = *reinterpret_cast<const float2*>(om + np * 32 + 16 * kk + 8 + 2 * tig);
                 }
-                fo[kk][0] = pack2(x0.x, x0.y);
+                fo[kk][0] = split_pack(x0.x, x0.y, false);
                 fo[kk][1] = split_pack(x0.x, x0.y, true);
-                fo[kk][2] = pack2(x1.x, x1.y);
+                fo[kk][2] = split_pack(x1.x, x1.y, false);
                 fo[kk][3] = split_pack(x1.x, x1.y, true);
             }
             WA_STAMP(9);
