@@ -307,6 +307,25 @@ def lm_arm(args, w, rank, world, local_rank):
             ms_step = timed(step, args.steps) / args.steps
             tokens, launches = w["B"] * w["L"], None
             h2d, d2h = ids.numel() * 8 * world, last.numel() * 2 * world
+            # share of the fused scan path in the step: the same scan_fused calls (4 rows x L tokens, one per
+            # layer and slice) on random tensors of the model's shapes, timed alone
+            from cdssm_b200 import ops
+            Hh, Nn, Dd = cfg.n_heads, cfg.state_dim, cfg.head_dim
+            rb = min(4, Bl)
+            sq, sk = (torch.randn(rb, w["L"], Hh, Dd, device=dev).bfloat16() for _ in range(2))
+            sv = torch.randn(rb, w["L"], Hh, Nn, device=dev).bfloat16()
+            sg = torch.randn(rb, w["L"], (Nn + 5) * Hh, device=dev).bfloat16()
+            p0 = lm.blocks[0]
+
+            def scans():
+                for _ in range(cfg.n_layers * ((Bl + rb - 1) // rb)):
+                    ops.scan_fused(sq, sk, sv, sg, p0.log_dt_scale, p0.rope_freqs, *cfg.dyn_consts, Hh, Nn, cfg.chunk_size)
+
+            scans()
+            scan_ms = timed(scans, args.steps) / args.steps
+            scan_share = {"scan_ms_per_step": scan_ms, "share": scan_ms / ms_step,
+                          "what": f"{cfg.n_layers * ((Bl + rb - 1) // rb)} scan_fused calls of ({rb},{w['L']},{Hh},{Dd}) per step, "
+                                  "timed alone on random inputs (tensor-core passes: head_dim 64, H a multiple of 4)"}
         else:
             dids = ids.to(dev)
             caches = []
@@ -351,6 +370,8 @@ def lm_arm(args, w, rank, world, local_rank):
                         "note": "the timed step already starts from host token ids / ends with host results"},
                 "gpu_launches": args.steps * cfg.n_layers * (2 if decode else 4),
                 "roofline": None}
+        if not decode:
+            line["scan_share"] = scan_share
         if decode:
             per_bh = 2 * N * D * 4 + 2 * D * 2 + (3 * N + 5) * 2
             line["decode_state_bytes_per_step"] = cfg.n_layers * w["B"] * H * per_bh / world

@@ -108,8 +108,46 @@ class CdssmBlockParams:
         self.shortcut_scale = 0.0
 
 
+    def load_reference(self, sd, prefix, device, dtype):
+        """Take this block's weights from a reference state dict (parameter names of
+        cdssm/models/block.py:35-88 under `prefix`, e.g. "blocks.3.")."""
+        to = lambda name: sd[prefix + name].to(device=device, dtype=dtype).contiguous()
+        f32 = lambda name: sd[prefix + name].to(device=device, dtype=torch.float32).contiguous()
+        self.norm_w = to("norm.weight")
+        self.w_in, self.b_in = to("in_proj.weight"), to("in_proj.bias")
+        self.conv_w, self.conv_b = to("conv.weight"), to("conv.bias")
+        self.w_gate, self.b_gate = to("gate_proj.weight"), to("gate_proj.bias")
+        self.log_dt_scale = f32("log_dt_scale")
+        self.w_q, self.w_readout, self.w_out = to("Q_proj.weight"), to("readout_proj.weight"), to("out_proj.weight")
+        self.gn_w, self.gn_b = to("ssm_norm.weight"), to("ssm_norm.bias")
+        self.D = to("D")
+        self.v_residual_gate = f32("v_residual_gate")
+        self.shortcut_scale = float(sd[prefix + "shortcut_scale"].float().item())
+
+
 class CdssmLM:
     """Embedding -> n_layers blocks -> RMSNorm -> tied LM head, inference only."""
+
+    @classmethod
+    def from_reference_checkpoint(cls, ckpt, device="cuda", dtype=torch.bfloat16):
+        """Build the model from a checkpoint of the reference trainer: a dict (or the path of a torch.save'd
+        dict) with "config" (the dataclass fields of cdssm/config/model.py; the derived ones are recomputed)
+        and "model_state_dict" (cdssm/training/trainer.py:205-214, read like cdssm/inference/predict.py:10-30,
+        including the "_orig_mod." prefix a compiled model leaves on its keys)."""
+        if isinstance(ckpt, (str, bytes)) or hasattr(ckpt, "__fspath__"):
+            ckpt = torch.load(ckpt, map_location="cpu", weights_only=False)
+        c = ckpt["config"]
+        cfg = CdssmConfig(**{k: c[k] for k in ("d_model", "n_layers", "context_length", "vocab_size", "state_dim")})
+        sd = {k.replace("_orig_mod.", ""): v for k, v in ckpt["model_state_dict"].items()}
+        lm = cls(cfg, device=device, dtype=dtype, seed=0)
+        lm.load_reference_state_dict(sd)
+        return lm
+
+    def load_reference_state_dict(self, sd):
+        self.embedding = sd["embedding.weight"].to(device=self.device, dtype=self.dtype).contiguous()
+        self.final_norm_w = sd["final_norm.weight"].to(device=self.device, dtype=self.dtype).contiguous()
+        for i, p in enumerate(self.blocks):
+            p.load_reference(sd, f"blocks.{i}.", self.device, self.dtype)
 
     def __init__(self, cfg: CdssmConfig, device="cuda", dtype=torch.bfloat16, seed=0):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
@@ -134,7 +172,8 @@ class CdssmLM:
         else:                                   # value residual across layers (block.py:167-171)
             nu = torch.sigmoid(p.v_residual_gate).to(V.dtype)
             V = torch.lerp(v_first, V, nu[None, None, :, None])
-        if cache is None or L > 1:
+        decoding = cache is not None and "state" in cache     # a populated cache: one-token step
+        if not decoding:
             x_conv = ops.CUDAConv1dSiLUOp.apply(x_gate.contiguous(), p.conv_w, p.conv_b)
             if cache is not None:               # last three inputs of the causal 4-tap conv
                 hist = torch.zeros(B, 3, di, device=x.device, dtype=x.dtype)
@@ -148,7 +187,7 @@ class CdssmLM:
             cache["conv"].copy_(win[:, 1:])     # in place: the cache tensors keep their addresses
         gates = F.linear(x_conv, p.w_gate, p.b_gate)
         Q = F.linear(x_conv, p.w_q).reshape(B, L, H, cfg.head_dim)
-        if cache is not None and L == 1:
+        if decoding:
             y = ops.decode_step(cache["state"], Q[:, 0], K[:, 0], V[:, 0], gates[:, 0], p.log_dt_scale,
                                 p.rope_freqs, *cfg.dyn_consts, H, N, pos0,
                                 shortcut_scale=p.shortcut_scale).unsqueeze(1)
@@ -205,19 +244,27 @@ class CdssmLM:
         The reference instead re-runs the whole window per token (cdssm/inference/predict.py:53-67)."""
         x = self.embedding[token_ids].unsqueeze(1)
         v_first = None
-        pos = cache.get("pos_dev", cache["pos"])   # a device int32 makes the step graph-replayable
+        # one position counter: the host integer, or - once a decode graph exists - the device int32 that
+        # makes the step graph-replayable (see position())
+        pos = cache["pos_dev"] if "pos_dev" in cache else cache["pos"]
         for p, c in zip(self.blocks, cache["layers"]):
             x, v_first = self._block(p, x, v_first, pos, c, 0)
-        cache["pos"] += 1
         if "pos_dev" in cache:
             cache["pos_dev"] += 1
+        else:
+            cache["pos"] += 1
         return F.linear(_rms_norm(x[:, 0], self.final_norm_w, 2.0 ** -14), self.embedding)
+
+    @staticmethod
+    def position(cache):
+        """Number of tokens the cache has seen (reads the device counter if a decode graph owns it)."""
+        return int(cache["pos_dev"].item()) if "pos_dev" in cache else int(cache["pos"])
 
     def make_decode_graph(self, cache, batch):
         """Capture one greedy decode step as a CUDA graph: static token buffer in, next tokens out,
         position in device memory.  Returns (graph, token_buffer); replay advances the cache."""
         dev = self.device
-        cache["pos_dev"] = torch.tensor([cache["pos"]], dtype=torch.int32, device=dev)
+        cache["pos_dev"] = torch.tensor([cache.pop("pos")], dtype=torch.int32, device=dev)
         tok = torch.zeros(batch, dtype=torch.int64, device=dev)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -229,10 +276,8 @@ class CdssmLM:
         for c, s0 in zip(cache["layers"], snapshot):
             for k in c:
                 c[k].copy_(s0[k])
-        cache["pos"] -= 2
         cache["pos_dev"] -= 2
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             tok.copy_(self.decode(tok, cache).argmax(-1))
-        cache["pos"] -= 1                            # the capture pass did not execute
         return graph, tok

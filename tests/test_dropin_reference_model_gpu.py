@@ -89,18 +89,8 @@ def test_reference_block_runs_on_our_operators(ops, N):
         lm = CdssmLM(CdssmConfig(d_model=128, n_layers=2, context_length=512, vocab_size=256, state_dim=N),
                      device="cuda", dtype=torch.bfloat16, seed=0)
         p = lm.blocks[1]
-        sd = state
-        p.norm_w = sd["norm.weight"]
-        p.w_in, p.b_in = sd["in_proj.weight"], sd["in_proj.bias"]
-        p.conv_w, p.conv_b = sd["conv.weight"], sd["conv.bias"]
-        p.w_gate, p.b_gate = sd["gate_proj.weight"], sd["gate_proj.bias"]
-        p.log_dt_scale = sd["log_dt_scale"].float()
+        p.load_reference(state, "", "cuda", torch.bfloat16)
         p.rope_freqs = blk.rope_freqs.float()
-        p.w_q, p.w_readout, p.w_out = sd["Q_proj.weight"], sd["readout_proj.weight"], sd["out_proj.weight"]
-        p.gn_w, p.gn_b = sd["ssm_norm.weight"], sd["ssm_norm.bias"]
-        p.D = sd["D"]
-        p.v_residual_gate = sd["v_residual_gate"].float()
-        p.shortcut_scale = float(sd["shortcut_scale"].float().item())
         with torch.no_grad():
             y_model, _ = lm._block(p, x, v_first, 0, None, 0)
             y_model0, _ = lm._block(p, x, None, 0, None, 0)
@@ -124,5 +114,39 @@ def test_reference_block_runs_on_our_operators(ops, N):
         assert rel_err(to_np(y_ours), to_np(y_ref)) <= BF16_TOL, "reference block on our operators differs"
         assert rel_err(to_np(y_ours0), to_np(y_ref0)) <= BF16_TOL
         assert rel_err(to_np(y_model), to_np(y_ref)) <= BF16_TOL
+    finally:
+        _purge()
+
+
+def test_reference_checkpoint_loads_and_matches_the_reference_lm(ops, tmp_path):
+    """A checkpoint in the reference trainer's format (trainer.py:205-214), written by the reference's own LM
+    class, loaded by CdssmLM.from_reference_checkpoint: same logits as the reference model on our operators."""
+    import dataclasses
+    root = _reference_root()
+    try:
+        _load_reference_models(root, ops_module=ops)
+        model_mod = importlib.import_module("cdssm.models.model")
+        cfg_mod = importlib.import_module("cdssm.config.model")
+        torch.manual_seed(3)
+        cfg = cfg_mod.CDSSMConfig(d_model=128, n_layers=3, context_length=256, vocab_size=512, state_dim=2)
+        ref_lm = model_mod.CDSSMLMHeadModel(cfg)
+        with torch.no_grad():
+            for blk in ref_lm.blocks:
+                blk.shortcut_scale.fill_(0.3)
+                blk.v_residual_gate.normal_()
+        path = tmp_path / "ckpt.pt"
+        torch.save({"model_state_dict": {"_orig_mod." + k: v for k, v in ref_lm.state_dict().items()},
+                    "config": dataclasses.asdict(cfg), "step": 7}, path)
+        ref_lm = ref_lm.cuda().bfloat16().eval()
+        for blk in ref_lm.blocks:
+            blk.rope_freqs = blk.rope_freqs.float()
+        ids = torch.randint(0, 512, (2, 150), generator=torch.Generator().manual_seed(4)).cuda()
+        with torch.no_grad():
+            want = ref_lm(ids).float()
+        from cdssm_b200.model import CdssmLM
+        lm = CdssmLM.from_reference_checkpoint(str(path))
+        assert (lm.cfg.n_layers, lm.cfg.n_heads, lm.cfg.state_dim) == (3, 4, 2)
+        got = lm.forward(ids).float()
+        assert rel_err(to_np(got), to_np(want)) <= 3e-2      # 3 layers of bf16 GEMMs and norms on top of the scan
     finally:
         _purge()

@@ -77,6 +77,23 @@ def test_graph_replayed_decode_equals_eager_decode(lm32):
         replayed.append(buf.clone())
     assert all(torch.equal(a, b) for a, b in zip(eager, replayed))
     assert torch.allclose(c1["layers"][-1]["state"], c2["layers"][-1]["state"], atol=1e-5)
+    # one position counter: the replays advanced it, and an eager step after the graph continues from there
+    assert lm32.position(c1) == 25 and lm32.position(c2) == 25
+    a = lm32.decode(eager[-1], c1)
+    b = lm32.decode(replayed[-1], c2)
+    assert torch.allclose(a, b, atol=1e-4) and lm32.position(c2) == 26
+
+
+def test_one_token_prompt(lm32):
+    """A prompt of a single token is a prefill (empty cache), not a decode step."""
+    ids = torch.tensor([[5], [9]], device="cuda")
+    logits, cache = lm32.prefill(ids)
+    assert logits.shape == (2, 1, 1000) and lm32.position(cache) == 1
+    nxt = lm32.decode(logits[:, -1].argmax(-1), cache)
+    lm32.per_token_group_norm = True
+    full = lm32.forward(torch.cat([ids, logits[:, -1].argmax(-1)[:, None]], 1)).float()
+    lm32.per_token_group_norm = False
+    assert (nxt.float() - full[:, 1]).abs().max() <= 2e-3 * full.abs().max()
 
 
 def test_forward_is_deterministic_and_batch_independent(lm):
