@@ -1,0 +1,241 @@
+// The memory-bound steps either side of the scan inside a CD-SSM block, one kernel each instead of the
+// handful of elementwise kernels an eager framework launches for them:
+//   RMSNorm                                   cdssm/models/modules.py:37-53
+//   GroupNorm -> * silu(z) -> + D * x_conv    cdssm/models/block.py:213-224
+//   one-token depthwise conv + SiLU on a cached three-row history (the decode-time form of conv1d_silu.cu:25-90)
+// Arithmetic in fp32; with bf16 storage every intermediate is rounded where the reference's eager bf16
+// operations round it, so the fused result equals the unfused one bit for bit except for the reduction order
+// of the statistics.
+#include "cdssm_common.cuh"
+
+namespace cdssm {
+
+template <typename T> struct Vec8;   // eight consecutive elements
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float* f) {
+        unpack8(*reinterpret_cast<const uint4*>(p), f);
+    }
+    static __device__ __forceinline__ void st(__nv_bfloat16* p, const float* f) {
+        uint4 r;
+        r.x = pack2(f[0], f[1]); r.y = pack2(f[2], f[3]); r.z = pack2(f[4], f[5]); r.w = pack2(f[6], f[7]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void ld(const float* p, float* f) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    static __device__ __forceinline__ void st(float* p, const float* f) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+};
+
+// ---------------------------------------------------------------- RMSNorm
+// One warp per row: out = rnd(rnd(x * rsqrt(mean x^2 + eps)) * w)   (modules.py:50-53)
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, long long rows, int d,
+                   float eps) {
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const T* xr = x + row * d;
+    float ss = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+        float f[8];
+        Vec8<T>::ld(xr + c, f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += f[e] * f[e];
+    }
+    const float rms = rsqrtf(warp_sum(ss) / (float)d + eps);
+    T* orow = out + row * d;
+    for (int c = lane * 8; c < d; c += 256) {
+        float f[8], g[8];
+        Vec8<T>::ld(xr + c, f);
+        Vec8<T>::ld(w + c, g);
+#pragma unroll
+        for (int e = 0; e < 8; e++) f[e] = IO<T>::rnd(f[e] * rms) * g[e];
+        Vec8<T>::st(orow + c, f);
+    }
+}
+
+// ---------------------------------------------------------------- GroupNorm statistics over a whole sequence
+// The reference normalises (B, d_inner, L): each group's statistics run over its channels AND all positions
+// (block.py:216-222).  One block per (batch row, group); fixed summation order, so the result is deterministic.
+template <typename T>
+__global__ void __launch_bounds__(256)
+groupnorm_stats_kernel(const T* __restrict__ y, float* __restrict__ stats, int L, int di, int groups, float eps) {
+    const int b = blockIdx.x / groups, grp = blockIdx.x % groups;
+    const int cg = di / groups, v8 = cg / 8;
+    const T* base = y + (long long)b * L * di + grp * cg;
+    const long long items = (long long)L * v8;
+    double s = 0.0, q = 0.0;
+    for (long long i = threadIdx.x; i < items; i += 256) {
+        const long long l = i / v8;
+        const int c = (int)(i % v8) * 8;
+        float f[8];
+        Vec8<T>::ld(base + l * di + c, f);
+        float ps = 0.f, pq = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) { ps += f[e]; pq += f[e] * f[e]; }
+        s += ps;
+        q += pq;
+    }
+    __shared__ double sh[2][256];
+    sh[0][threadIdx.x] = s;
+    sh[1][threadIdx.x] = q;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) {
+            sh[0][threadIdx.x] += sh[0][threadIdx.x + o];
+            sh[1][threadIdx.x] += sh[1][threadIdx.x + o];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const double n = (double)L * cg, mean = sh[0][0] / n;
+        const double var = fmax(sh[1][0] / n - mean * mean, 0.0);
+        stats[2 * blockIdx.x] = (float)mean;
+        stats[2 * blockIdx.x + 1] = (float)(1.0 / sqrt(var + (double)eps));
+    }
+}
+
+// ---------------------------------------------------------------- GroupNorm + gate + skip
+// One block per token, one thread per eight channels.  stats == NULL: statistics per token and group (the
+// causal form used with a decode cache); otherwise mean / rstd of the token's (batch row, group) from
+// groupnorm_stats_kernel.  out = rnd(rnd(rnd(GN(y)) * rnd(silu(z))) + rnd(D * x_conv))   (block.py:216-224)
+template <typename T>
+__global__ void __launch_bounds__(1024)
+groupnorm_gate_fwd_kernel(const T* __restrict__ y, const float* __restrict__ stats, const T* __restrict__ gn_w,
+                          const T* __restrict__ gn_b, const T* __restrict__ z, long long z_row_stride,
+                          const T* __restrict__ skip, const T* __restrict__ x_conv, T* __restrict__ out, int L,
+                          int di, int groups, float eps) {
+    const long long row = blockIdx.x;
+    const int c = threadIdx.x * 8;
+    const int cg = di / groups, tpg = cg / 8;          // threads per group
+    const int grp = threadIdx.x / tpg;
+    float f[8];
+    Vec8<T>::ld(y + row * di + c, f);
+    float mean, rstd;
+    if (stats == nullptr) {
+        __shared__ float sh[2][1024];
+        float ps = 0.f, pq = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) { ps += f[e]; pq += f[e] * f[e]; }
+        sh[0][threadIdx.x] = ps;
+        sh[1][threadIdx.x] = pq;
+        __syncthreads();
+        float s = 0.f, q = 0.f;
+        for (int i = 0; i < tpg; i++) { s += sh[0][grp * tpg + i]; q += sh[1][grp * tpg + i]; }
+        mean = s / (float)cg;
+        rstd = rsqrtf(fmaxf(q / (float)cg - mean * mean, 0.f) + eps);
+    } else {
+        const long long b = row / L;
+        mean = stats[2 * (b * groups + grp)];
+        rstd = stats[2 * (b * groups + grp) + 1];
+    }
+    float gw[8], gb[8], zz[8], sk[8], xc[8];
+    Vec8<T>::ld(gn_w + c, gw);
+    Vec8<T>::ld(gn_b + c, gb);
+    Vec8<T>::ld(z + row * z_row_stride + c, zz);
+    Vec8<T>::ld(skip + c, sk);
+    Vec8<T>::ld(x_conv + row * di + c, xc);
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float n = IO<T>::rnd((f[e] - mean) * rstd * gw[e] + gb[e]);
+        const float g = IO<T>::rnd(siluf_<false>(zz[e]));
+        f[e] = IO<T>::rnd(n * g) + IO<T>::rnd(sk[e] * xc[e]);
+    }
+    Vec8<T>::st(out + row * di + c, f);
+}
+
+// ---------------------------------------------------------------- one-token conv + SiLU on a cached history
+// hist (B,3,Dm): the last three inputs of the causal 4-tap depthwise conv, updated in place.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv1d_silu_step_kernel(const T* __restrict__ x, long long x_row_stride, T* __restrict__ hist,
+                        const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ out, int B, int Dm) {
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (long long)B * Dm) return;
+    const int d = (int)(idx % Dm);
+    const long long b = idx / Dm;
+    T* h = hist + b * 3 * Dm + d;
+    const float x0 = IO<T>::ld(h), x1 = IO<T>::ld(h + Dm), x2 = IO<T>::ld(h + 2 * Dm);
+    const float x3 = IO<T>::ld(x + b * x_row_stride + d);
+    const float yv = IO<T>::ld(w + d * 4) * x0 + IO<T>::ld(w + d * 4 + 1) * x1 + IO<T>::ld(w + d * 4 + 2) * x2 +
+                     IO<T>::ld(w + d * 4 + 3) * x3 + IO<T>::ld(bias + d);
+    IO<T>::st(out + b * Dm + d, siluf_<IO<T>::kBf16>(yv));
+    IO<T>::st(h, x1);
+    IO<T>::st(h + Dm, x2);
+    IO<T>::st(h + 2 * Dm, x3);
+}
+
+}  // namespace cdssm
+
+using namespace cdssm;
+
+#define DISPATCH_DTYPE(dtype, ...)                                 \
+    if ((dtype) == CDSSM_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else if ((dtype) == CDSSM_F32) { using T = float; __VA_ARGS__; }     \
+    else return CDSSM_ERR_BAD_ARG;
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+extern "C" int cdssm_b200_rmsnorm_fwd(const void* x, const void* weight, void* out, int64_t rows, int d, float eps,
+                                      int dtype, void* stream) {
+    if (!x || !weight || !out || rows < 0 || d <= 0) return CDSSM_ERR_BAD_ARG;
+    if (d % 8 || !aligned16(x) || !aligned16(weight) || !aligned16(out)) return CDSSM_ERR_UNSUPPORTED;
+    if (rows == 0) return CDSSM_OK;
+    const unsigned blocks = (unsigned)((rows + 7) / 8);
+    DISPATCH_DTYPE(dtype, (rmsnorm_fwd_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+                              (const T*)x, (const T*)weight, (T*)out, rows, d, eps)));
+    return check_launch();
+}
+
+static int check_gn(int di, int groups) {
+    if (di <= 0 || groups <= 0 || di % groups) return CDSSM_ERR_BAD_ARG;
+    if ((di / groups) % 8 || di / 8 > 1024) return CDSSM_ERR_UNSUPPORTED;
+    return CDSSM_OK;
+}
+
+extern "C" int cdssm_b200_groupnorm_stats(const void* y, float* stats, int B, int L, int di, int groups, float eps,
+                                          int dtype, void* stream) {
+    if (!y || !stats || B < 0 || L < 0) return CDSSM_ERR_BAD_ARG;
+    if (int rc = check_gn(di, groups)) return rc;
+    if (!aligned16(y)) return CDSSM_ERR_UNSUPPORTED;
+    if (B == 0 || L == 0) return CDSSM_OK;
+    DISPATCH_DTYPE(dtype, (groupnorm_stats_kernel<T><<<(unsigned)(B * groups), 256, 0, (cudaStream_t)stream>>>(
+                              (const T*)y, stats, L, di, groups, eps)));
+    return check_launch();
+}
+
+extern "C" int cdssm_b200_groupnorm_gate_fwd(const void* y, const float* stats, const void* gn_weight,
+                                             const void* gn_bias, const void* z, int64_t z_row_stride,
+                                             const void* skip, const void* x_conv, void* out, int B, int L, int di,
+                                             int groups, float eps, int dtype, void* stream) {
+    if (!y || !gn_weight || !gn_bias || !z || !skip || !x_conv || !out || B < 0 || L < 0) return CDSSM_ERR_BAD_ARG;
+    if (int rc = check_gn(di, groups)) return rc;
+    const size_t es = dtype == CDSSM_F32 ? 4 : 2;
+    if (!aligned16(y) || !aligned16(z) || !aligned16(x_conv) || !aligned16(out) || !aligned16(gn_weight) ||
+        !aligned16(gn_bias) || !aligned16(skip) || (z_row_stride * es) % 16)
+        return CDSSM_ERR_UNSUPPORTED;
+    const long long rows = (long long)B * L;
+    if (rows == 0) return CDSSM_OK;
+    if (rows > 0x7fffffffLL) return CDSSM_ERR_UNSUPPORTED;
+    DISPATCH_DTYPE(dtype, (groupnorm_gate_fwd_kernel<T><<<(unsigned)rows, di / 8, 0, (cudaStream_t)stream>>>(
+                              (const T*)y, stats, (const T*)gn_weight, (const T*)gn_bias, (const T*)z, z_row_stride,
+                              (const T*)skip, (const T*)x_conv, (T*)out, L, di, groups, eps)));
+    return check_launch();
+}
+
+extern "C" int cdssm_b200_conv1d_silu_step(const void* x, int64_t x_row_stride, void* hist, const void* weight,
+                                           const void* bias, void* out, int B, int Dm, int dtype, void* stream) {
+    if (!x || !hist || !weight || !bias || !out || B < 0 || Dm <= 0) return CDSSM_ERR_BAD_ARG;
+    if (B == 0) return CDSSM_OK;
+    const long long n = (long long)B * Dm;
+    DISPATCH_DTYPE(dtype, (conv1d_silu_step_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                              (const T*)x, x_row_stride, (T*)hist, (const T*)weight, (const T*)bias, (T*)out, B, Dm)));
+    return check_launch();
+}

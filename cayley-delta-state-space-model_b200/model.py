@@ -53,6 +53,8 @@ class CdssmConfig:
 
 
 def _rms_norm(x, weight, eps):
+    if x.shape[-1] % 8 == 0:
+        return ops.rms_norm(x, weight, eps)           # one kernel
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
 
@@ -180,11 +182,8 @@ class CdssmLM:
                 n = min(3, L)
                 hist[:, 3 - n:] = x_gate[:, L - n:]
                 cache["conv"] = hist
-        else:                                   # decode: one output from the cached history
-            win = torch.cat([cache["conv"], x_gate], dim=1)                    # (B,4,di)
-            w = p.conv_w.view(di, 4).float()
-            x_conv = F.silu((win.float() * w.t()[None]).sum(1) + p.conv_b.float()).to(x.dtype).unsqueeze(1)
-            cache["conv"].copy_(win[:, 1:])     # in place: the cache tensors keep their addresses
+        else:                                   # decode: one output from the cached history, shifted in place
+            x_conv = ops.conv1d_silu_step(x_gate[:, 0], cache["conv"], p.conv_w, p.conv_b).unsqueeze(1)
         gates = F.linear(x_conv, p.w_gate, p.b_gate)
         Q = F.linear(x_conv, p.w_q).reshape(B, L, H, cfg.head_dim)
         if decoding:
@@ -204,13 +203,17 @@ class CdssmLM:
         # (block.py:216-222: group_norm on (B, d_inner, L)), which makes its forward non-causal.  A
         # cached decode cannot reproduce that, so the prefill/decode path - and forward() when
         # per_token_group_norm is set - takes the statistics per token instead.
-        if cache is not None or self.per_token_group_norm:
-            y = F.group_norm(y.float().reshape(B * L, di, 1), cfg.ssm_norm_groups, p.gn_w.float(),
-                             p.gn_b.float(), 1e-5).to(x.dtype).reshape(B, L, di)
+        per_token = cache is not None or self.per_token_group_norm
+        if (di // cfg.ssm_norm_groups) % 8 == 0 and di <= 8192:
+            y = ops.groupnorm_gate(y, p.gn_w, p.gn_b, z, p.D, x_conv, cfg.ssm_norm_groups, 1e-5, per_token=per_token)
         else:
-            y = F.group_norm(y.float().transpose(1, 2), cfg.ssm_norm_groups, p.gn_w.float(), p.gn_b.float(),
-                             1e-5).to(x.dtype).transpose(1, 2)
-        y = y * F.silu(z) + p.D * x_conv
+            if per_token:
+                y = F.group_norm(y.float().reshape(B * L, di, 1), cfg.ssm_norm_groups, p.gn_w.float(),
+                                 p.gn_b.float(), 1e-5).to(x.dtype).reshape(B, L, di)
+            else:
+                y = F.group_norm(y.float().transpose(1, 2), cfg.ssm_norm_groups, p.gn_w.float(), p.gn_b.float(),
+                                 1e-5).to(x.dtype).transpose(1, 2)
+            y = y * F.silu(z) + p.D * x_conv
         return x + F.linear(y, p.w_out), v_first
 
     # ------------------------------------------------------------------ public API

@@ -21,7 +21,7 @@ from ._lib import CdssmError, check
 
 __all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
            "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
-           "scan_fused_workspace_bytes", "scan_fused_status", "set_wait_limit_ns", "selftest_bounded_wait", "scan_summary", "scan_fused_long", "compose_carries",
+           "scan_fused_workspace_bytes", "scan_fused_status", "set_wait_limit_ns", "selftest_bounded_wait", "rms_norm", "groupnorm_gate", "conv1d_silu_step", "scan_summary", "scan_fused_long", "compose_carries",
            "CdssmError"]
 
 _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
@@ -354,6 +354,64 @@ def scan_fused_status(device=None) -> int:
     if rc not in (0, -5):
         check(rc, "scan_fused_status")
     return out.value
+
+
+def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    """RMSNorm over the last dimension in one kernel (cdssm/models/modules.py:50-53)."""
+    x = _prep(x, name="x")
+    w = _prep(weight, dtype=x.dtype, name="weight")
+    d = x.shape[-1]
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(_lib.lib().cdssm_b200_rmsnorm_fwd(_p(x), _p(w), _p(out), x.numel() // d, d, float(eps),
+                                                _dtype_code(x), _stream()), "rmsnorm_fwd")
+    return out
+
+
+def groupnorm_gate(y: Tensor, gn_weight: Tensor, gn_bias: Tensor, z: Tensor, skip: Tensor, x_conv: Tensor,
+                   groups: int, eps: float = 1e-5, per_token: bool = False) -> Tensor:
+    """GroupNorm(y) * silu(z) + skip * x_conv for (B,L,di) tensors (cdssm/models/block.py:213-224) in two kernels
+    (statistics over channels x all positions, as the reference takes them) or, with per_token=True, in one
+    (statistics per token: the causal form used with a decode cache).  z may be a column slice of a wider
+    projection (rows strided)."""
+    y = _prep(y, name="y")
+    xc = _prep(x_conv, dtype=y.dtype, name="x_conv")
+    B, L, di = y.shape
+    if not z.is_cuda or z.dtype != y.dtype or tuple(z.shape) != (B, L, di) or z.stride(-1) != 1 or \
+            (L > 1 and z.stride(0) != L * z.stride(1)):
+        z = z.contiguous()
+    zs = z.stride(1) if L > 1 else (z.stride(0) if B > 1 else di)
+    if (zs * z.element_size()) % 16 or z.data_ptr() % 16:      # the kernel reads 16-byte pieces
+        z, zs = z.contiguous(), di
+    gw, gb, sk = (_prep(t, dtype=y.dtype, name="groupnorm parameter") for t in (gn_weight, gn_bias, skip))
+    out = torch.empty_like(y)
+    with torch.cuda.device(y.device):
+        stats = None
+        if not per_token:
+            stats = torch.empty(B, groups, 2, dtype=torch.float32, device=y.device)
+            check(_lib.lib().cdssm_b200_groupnorm_stats(_p(y), _p(stats), B, L, di, int(groups), float(eps),
+                                                        _dtype_code(y), _stream()), "groupnorm_stats")
+        check(_lib.lib().cdssm_b200_groupnorm_gate_fwd(_p(y), _p(stats), _p(gw), _p(gb), _p(z), zs, _p(sk), _p(xc),
+                                                       _p(out), B, L, di, int(groups), float(eps), _dtype_code(y),
+                                                       _stream()), "groupnorm_gate_fwd")
+    return out
+
+
+def conv1d_silu_step(x: Tensor, hist: Tensor, weight: Tensor, bias: Tensor) -> Tensor:
+    """One position of the causal depthwise conv + SiLU: x (B,Dm) (rows may be strided), hist (B,3,Dm) the last
+    three inputs, shifted in place.  Returns (B,Dm)."""
+    if not x.is_cuda or x.stride(-1) != 1:
+        x = x.contiguous()
+    B, Dm = x.shape
+    if hist.dtype != x.dtype or not hist.is_contiguous() or tuple(hist.shape) != (B, 3, Dm):
+        raise CdssmError("conv1d_silu_step: hist must be a contiguous (B,3,Dm) tensor of the input dtype")
+    w = _prep(weight, dtype=x.dtype, name="weight")
+    b = _prep(bias, dtype=x.dtype, name="bias")
+    out = torch.empty(B, Dm, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_lib.lib().cdssm_b200_conv1d_silu_step(_p(x), x.stride(0) if B > 1 else Dm, _p(hist), _p(w), _p(b),
+                                                     _p(out), B, Dm, _dtype_code(x), _stream()), "conv1d_silu_step")
+    return out
 
 
 def set_wait_limit_ns(limit_ns: int) -> int:

@@ -88,6 +88,35 @@ CDSSM_API int cdssm_b200_exact_correction_fwd(const void* A, const void* K, cons
 CDSSM_API int cdssm_b200_conv1d_silu_fwd(const void* x, const void* weight, const void* bias, void* out,
                                int B, int L, int Dm, int dtype, void* stream);
 
+/* ---- block glue: the memory-bound steps either side of the scan, one kernel each -------------------- */
+
+/* RMSNorm over the last dimension: out = (x * rsqrt(mean(x^2) + eps)) * weight, rows x d, d a multiple of 8,
+ * 16-byte aligned buffers (CDSSM_ERR_UNSUPPORTED otherwise).
+ * Replaces RMSNorm.forward, cdssm/models/modules.py:50-53 (four eager kernels). */
+CDSSM_API int cdssm_b200_rmsnorm_fwd(const void* x, const void* weight, void* out, int64_t rows, int d, float eps,
+                                     int dtype, void* stream);
+
+/* GroupNorm statistics of y (B,L,di) taken over each group's channels and ALL L positions, as the reference's
+ * group_norm on (B, d_inner, L) does (cdssm/models/block.py:216-222): stats (B,groups,2) float32 = mean, rstd. */
+CDSSM_API int cdssm_b200_groupnorm_stats(const void* y, float* stats, int B, int L, int di, int groups, float eps,
+                                         int dtype, void* stream);
+
+/* out = GroupNorm(y) * silu(z) + skip * x_conv for y, x_conv, out (B,L,di) contiguous and z (B,L,di) with
+ * z_row_stride elements between rows (z is a column slice of the input projection).  stats from
+ * cdssm_b200_groupnorm_stats, or NULL: statistics per token and group (the causal form a decode cache needs).
+ * di / groups a multiple of 8, di <= 8192.  Replaces cdssm/models/block.py:213-224 (about ten eager kernels). */
+CDSSM_API int cdssm_b200_groupnorm_gate_fwd(const void* y, const float* stats, const void* gn_weight,
+                                            const void* gn_bias, const void* z, int64_t z_row_stride,
+                                            const void* skip, const void* x_conv, void* out, int B, int L, int di,
+                                            int groups, float eps, int dtype, void* stream);
+
+/* One position of the causal depthwise 4-tap conv + SiLU from a cached history: hist (B,3,Dm) holds the last three
+ * inputs and is shifted in place; x (B,Dm) with x_row_stride elements between rows; out (B,Dm).
+ * The decode-time form of conv1d_silu_fwd_cuda (cdssm/csrc/kernels/conv1d_silu.cu:25-90); the reference has no
+ * cached decode (cdssm/inference/predict.py:53-67 re-runs the window). */
+CDSSM_API int cdssm_b200_conv1d_silu_step(const void* x, int64_t x_row_stride, void* hist, const void* weight,
+                                          const void* bias, void* out, int B, int Dm, int dtype, void* stream);
+
 /* ---- the fused path -------------------------------------------------------------------- */
 
 /* Flags of cdssm_b200_scan_fused_fwd. */
