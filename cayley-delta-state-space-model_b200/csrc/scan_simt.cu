@@ -600,6 +600,8 @@ namespace cdssm {
 // state (read + write), everything else is a few hundred bytes per head.
 struct DecodeArgs {
     float* state;
+    float *corr, *carry, *gamma;   // reference-compatible step only: correction, carry (B,H,N,D), chunk decay (B,H,N)
+    int C;                         // chunk length of the reference-compatible step
     const void *q, *k, *v, *gate_raw;
     const float *log_dt_scale, *rope_freqs;
     void* y;
@@ -716,10 +718,170 @@ decode_step_kernel(const DecodeArgs a) {
     }
 }
 
+// The decode step that reproduces the reference's CHUNKED scan token by token (its outputs beyond the first
+// chunk are not those of the plain recurrence): per (batch, head) the local state z (zero at every chunk start),
+// the correction r (starts from the rounded carry, erase + rotate only, read before its step), the carry s
+// and the cumulative decay of the current chunk.  Position pos counts from the sequence start; chunks are
+// C tokens.  Same thread mapping as decode_step_kernel.
+template <typename T, int kCols>
+__global__ void __launch_bounds__(kSimtThreads)
+decode_step_ref_kernel(const DecodeArgs a) {
+    const int g = threadIdx.x % kLanesPerUnit;
+    long long u = (long long)blockIdx.x * kUnitsPerBlock + threadIdx.x / kLanesPerUnit;
+    const bool active = u < a.units;
+    if (!active) u = a.units - 1;
+    const int NH = a.N >> 1, D = a.D, H = a.H;
+    const int j = (int)(u % NH);
+    const int hd = (int)((u / NH) % H);
+    const long long b = u / ((long long)NH * H);
+    const bool vec = (D == kCols * kLanesPerUnit);
+    const long long bh = b * H + hd;
+
+    RowSlice<T, kCols> kraw, qraw;
+    kraw.load(static_cast<const T*>(a.k) + bh * D, g, D, vec);
+    qraw.load(static_cast<const T*>(a.q) + bh * D, g, D, vec);
+    const long long so = (bh * a.N + 2 * j) * D;
+    float* st = a.state + so;
+    float* ct = a.corr + so;
+    float zr[kCols], zi[kCols], rr[kCols], ri[kCols];
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < kCols / 4; i++) {
+            const float4 x = *reinterpret_cast<const float4*>(st + g * kCols + 4 * i);
+            const float4 w = *reinterpret_cast<const float4*>(st + D + g * kCols + 4 * i);
+            zr[4 * i] = x.x; zr[4 * i + 1] = x.y; zr[4 * i + 2] = x.z; zr[4 * i + 3] = x.w;
+            zi[4 * i] = w.x; zi[4 * i + 1] = w.y; zi[4 * i + 2] = w.z; zi[4 * i + 3] = w.w;
+            const float4 p = *reinterpret_cast<const float4*>(ct + g * kCols + 4 * i);
+            const float4 r = *reinterpret_cast<const float4*>(ct + D + g * kCols + 4 * i);
+            rr[4 * i] = p.x; rr[4 * i + 1] = p.y; rr[4 * i + 2] = p.z; rr[4 * i + 3] = p.w;
+            ri[4 * i] = r.x; ri[4 * i + 1] = r.y; ri[4 * i + 2] = r.z; ri[4 * i + 3] = r.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int d = g * kCols + i;
+            zr[i] = d < D ? st[d] : 0.f;
+            zi[i] = d < D ? st[D + d] : 0.f;
+            rr[i] = d < D ? ct[d] : 0.f;
+            ri[i] = d < D ? ct[D + d] : 0.f;
+        }
+    }
+    // dynamics (every lane of the unit computes the same scalars; dynamics_fused.cu:64-139)
+    const T* gr = static_cast<const T*>(a.gate_raw) + b * (long long)((a.N + 5) * H);
+    const T* s5 = gr + a.N * H;
+    const float freq = a.rope_freqs[hd], pos = (float)(a.pos_dev ? *a.pos_dev : a.pos);
+    DynShared ds = dyn_shared<IO<T>::kBf16>(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd), IO<T>::ld(s5 + hd),
+                              IO<T>::ld(s5 + H + hd), IO<T>::ld(s5 + 2 * H + hd),
+                              IO<T>::ld(s5 + 3 * H + hd), IO<T>::ld(s5 + 4 * H + hd),
+                              a.log_dt_scale[hd], freq, pos, a.dc);
+    float a_re, a_im, vp;
+    dyn_pair<IO<T>::kBf16>(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds, a_re, a_im, vp);
+    a_re = IO<T>::rnd(a_re);
+    a_im = IO<T>::rnd(a_im);
+    vp = IO<T>::rnd(vp);
+    const float be = IO<T>::rnd(ds.beta), sc = IO<T>::rnd(ds.sel_c);
+    const T* vrow = static_cast<const T*>(a.v) + bh * a.N + 2 * j;
+    const float vr = IO<T>::rnd(IO<T>::ld(vrow) * vp), vi = IO<T>::rnd(IO<T>::ld(vrow + 1) * vp);
+
+    float kk[kCols], qq[kCols];
+    kraw.get(kk);
+    qraw.get(qq);
+    normalise<T, kCols>(kk);
+    normalise<T, kCols>(qq);
+    float ur = 0.f, ui = 0.f, wr = 0.f, wi = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCols; i++) {
+        ur += zr[i] * kk[i]; ui += zi[i] * kk[i];
+        wr += rr[i] * kk[i]; wi += ri[i] * kk[i];
+    }
+    ur = be * group_sum(ur);
+    ui = be * group_sum(ui);
+    wr = be * group_sum(wr);
+    wi = be * group_sum(wi);
+    const float ivr = be * vr, ivi = be * vi;
+    float yr = 0.f, yi = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCols; i++) {
+        const float er = zr[i] - ur * kk[i], ei = zi[i] - ui * kk[i];
+        zr[i] = a_re * er - a_im * ei + ivr * kk[i];
+        zi[i] = a_re * ei + a_im * er + ivi * kk[i];
+        // the correction is read BEFORE its step (exact_correction.cu:90-94), then erased and rotated
+        yr += (zr[i] + rr[i]) * qq[i];
+        yi += (zi[i] + ri[i]) * qq[i];
+        const float cr = rr[i] - wr * kk[i], ci = ri[i] - wi * kk[i];
+        rr[i] = a_re * cr - a_im * ci;
+        ri[i] = a_re * ci + a_im * cr;
+    }
+    yr = group_sum(yr);
+    yi = group_sum(yi);
+    if (a.shortcut_scale != 0.f) {
+        float qk = 0.f;
+#pragma unroll
+        for (int i = 0; i < kCols; i++) qk += qq[i] * kk[i];
+        qk = group_sum(qk);
+        const float f = a.shortcut_scale * qk * qk;
+        yr += f * vr;
+        yi += f * vi;
+    }
+    if (!active) return;
+    // cumulative decay of the chunk; at the chunk's last token the carry takes the (rounded) chunk results, the
+    // local state restarts from zero and the correction from the (rounded) carry (inter_chunk_scan.cu:52-84)
+    float* gm = a.gamma + bh * a.N + 2 * j;
+    const float g0 = gm[0], g1 = gm[1];
+    float gr_ = a_re * g0 - a_im * g1, gi_ = a_re * g1 + a_im * g0;
+    const int posi = a.pos_dev ? *a.pos_dev : a.pos;
+    if (posi % a.C == a.C - 1) {
+        float* cy = a.carry + so;
+        const float dr = IO<T>::rnd(gr_), di = IO<T>::rnd(gi_);
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int d = g * kCols + i;
+            if (d < D) {
+                const float sr = cy[d], si = cy[D + d];
+                const float nr = dr * sr - di * si + IO<T>::rnd(zr[i]), ni = dr * si + di * sr + IO<T>::rnd(zi[i]);
+                cy[d] = nr;
+                cy[D + d] = ni;
+                rr[i] = IO<T>::rnd(nr);
+                ri[i] = IO<T>::rnd(ni);
+            }
+            zr[i] = 0.f;
+            zi[i] = 0.f;
+        }
+        gr_ = 1.f;
+        gi_ = 0.f;
+    }
+    if (g == 0) { gm[0] = gr_; gm[1] = gi_; }
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < kCols / 4; i++) {
+            *reinterpret_cast<float4*>(st + g * kCols + 4 * i) =
+                make_float4(zr[4 * i], zr[4 * i + 1], zr[4 * i + 2], zr[4 * i + 3]);
+            *reinterpret_cast<float4*>(st + D + g * kCols + 4 * i) =
+                make_float4(zi[4 * i], zi[4 * i + 1], zi[4 * i + 2], zi[4 * i + 3]);
+            *reinterpret_cast<float4*>(ct + g * kCols + 4 * i) =
+                make_float4(rr[4 * i], rr[4 * i + 1], rr[4 * i + 2], rr[4 * i + 3]);
+            *reinterpret_cast<float4*>(ct + D + g * kCols + 4 * i) =
+                make_float4(ri[4 * i], ri[4 * i + 1], ri[4 * i + 2], ri[4 * i + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kCols; i++) {
+            const int d = g * kCols + i;
+            if (d < D) { st[d] = zr[i]; st[D + d] = zi[i]; ct[d] = rr[i]; ct[D + d] = ri[i]; }
+        }
+    }
+    if (g == 0) {
+        T* o = static_cast<T*>(a.y) + bh * a.N + 2 * j;
+        IO<T>::st(o, IO<T>::rnd(yr) * sc);
+        IO<T>::st(o + 1, IO<T>::rnd(yi) * sc);
+    }
+}
+
 template <typename T, int kCols>
 static int launch_decode(const DecodeArgs& a, cudaStream_t st) {
     const unsigned blocks = (unsigned)((a.units + kUnitsPerBlock - 1) / kUnitsPerBlock);
-    decode_step_kernel<T, kCols><<<blocks, kSimtThreads, 0, st>>>(a);
+    if (a.corr) decode_step_ref_kernel<T, kCols><<<blocks, kSimtThreads, 0, st>>>(a);
+    else decode_step_kernel<T, kCols><<<blocks, kSimtThreads, 0, st>>>(a);
     return check_launch();
 }
 
@@ -853,9 +1015,11 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
                             const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
                             void* y, float gating_c, float omega_thresh, float adt_delta,
                             float adt_smoothness, float adt_eps, float shortcut_scale, int B, int H, int D,
-                            int N, int pos, const int* pos_dev, int dtype, void* stream) {
+                            int N, int pos, const int* pos_dev, int dtype, void* stream, float* corr = nullptr,
+                            float* carry = nullptr, float* gamma = nullptr, int C = 0) {
     if (!state || !q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y)
         return CDSSM_ERR_BAD_ARG;
+    if (corr && (!carry || !gamma || C <= 0 || (((uintptr_t)corr | (uintptr_t)carry) & 15))) return CDSSM_ERR_BAD_ARG;
     if (B < 0 || H <= 0 || D <= 0 || N <= 0 || (N & 1)) return CDSSM_ERR_BAD_ARG;
     if (dtype != CDSSM_BF16 && dtype != CDSSM_F32) return CDSSM_ERR_BAD_ARG;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)state) & 15) return CDSSM_ERR_BAD_ARG;
@@ -863,6 +1027,7 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
     if (B == 0) return CDSSM_OK;
     DecodeArgs a;
     a.state = state; a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
+    a.corr = corr; a.carry = carry; a.gamma = gamma; a.C = C;
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.y = y;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
     a.shortcut_scale = shortcut_scale;
@@ -1007,4 +1172,17 @@ extern "C" int cdssm_b200_decode_step_at(float* state, const void* q, const void
     return decode_step_impl(state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
                             adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, 0, pos_dev,
                             dtype, stream);
+}
+
+extern "C" int cdssm_b200_decode_step_reference(float* local_state, float* correction, float* carry, float* chunk_decay,
+                                                const void* q, const void* k, const void* v, const void* gate_raw,
+                                                const float* log_dt_scale, const float* rope_freqs, void* y,
+                                                float gating_c, float omega_thresh, float adt_delta,
+                                                float adt_smoothness, float adt_eps, float shortcut_scale, int B,
+                                                int H, int D, int N, int C, int pos, const int* pos_dev, int dtype,
+                                                void* stream) {
+    if (!correction || !carry || !chunk_decay || C <= 0 || pos < 0) return CDSSM_ERR_BAD_ARG;
+    return decode_step_impl(local_state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
+                            adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, pos, pos_dev, dtype,
+                            stream, correction, carry, chunk_decay, C);
 }

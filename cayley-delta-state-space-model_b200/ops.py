@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import CdssmError, check
 
 __all__ = ["CUDAConv1dSiLUOp", "DynamicsFusedFn", "NormalizeKQFn", "IntraChunkScanFn",
-           "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step",
+           "InterChunkScanFn", "ExactCorrectionFn", "scan_fused", "decode_step", "decode_step_reference", "reference_decode_state",
            "scan_fused_workspace_bytes", "scan_fused_status", "set_wait_limit_ns", "selftest_bounded_wait", "rms_norm", "groupnorm_gate", "conv1d_silu_step", "scan_summary", "scan_fused_long", "compose_carries",
            "CdssmError"]
 
@@ -334,6 +334,53 @@ def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor
             _p(state), _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh,
             adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, int(pos), _dtype_code(q),
             _stream()), "decode_step")
+    return y
+
+
+def reference_decode_state(carry: Tensor, dtype=torch.bfloat16):
+    """State of :func:`decode_step_reference` at a chunk boundary from the carry (B,H,N,D) float32 that
+    scan_fused returned as final_state (or zeros at the start of a sequence): a dict of the local state, the
+    correction (the carry rounded to the storage type), the carry and the chunk's cumulative decay."""
+    carry = _prep(carry, dtype=torch.float32, name="carry").clone()
+    B, H, N, D = carry.shape
+    gamma = torch.zeros(B, H, N, dtype=torch.float32, device=carry.device)
+    gamma[..., 0::2] = 1.0
+    return {"local": torch.zeros_like(carry), "correction": carry.to(dtype).float().clone(), "carry": carry, "decay": gamma}
+
+
+def decode_step_reference(state: dict, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor,
+                          rope_freqs: Tensor, gating_c: float, omega_thresh: float, adt_delta: float,
+                          adt_smoothness: float, adt_eps: float, n_heads: int, state_dim: int, chunk_size: int,
+                          pos, *, shortcut_scale: float = 0.0, out: Tensor = None) -> Tensor:
+    """One token of the reference's CHUNKED scan (see cdssm_b200_decode_step_reference): unlike
+    :func:`decode_step`, T of these steps reproduce scan_fused / the reference forward over T tokens for any T.
+    ``state`` comes from :func:`reference_decode_state` and is updated in place; ``pos`` is the token's position
+    from the start of the sequence (int, or an int32 CUDA tensor for graph replay)."""
+    q = _prep(q, name="q")
+    k = _prep(k, dtype=q.dtype, name="k")
+    v = _prep(v, dtype=q.dtype, name="v")
+    g = _prep(gate_raw, dtype=q.dtype, name="gate_raw")
+    B, H, D = q.shape
+    N = int(state_dim)
+    for name in ("local", "correction", "carry"):
+        t = state[name]
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != (B, H, N, D):
+            raise CdssmError(f"decode_step_reference: state['{name}'] must be a contiguous float32 (B,H,N,D) CUDA tensor")
+    if tuple(state["decay"].shape) != (B, H, N) or state["decay"].dtype != torch.float32:
+        raise CdssmError("decode_step_reference: state['decay'] must be float32 (B,H,N)")
+    if H != int(n_heads) or tuple(v.shape) != (B, H, N) or tuple(g.shape) != (B, (N + 5) * H):
+        raise CdssmError("decode_step_reference: inconsistent shapes")
+    lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
+    y = out if out is not None else torch.empty(B, H, N, dtype=q.dtype, device=q.device)
+    pos_dev, pos_i = (pos, 0) if isinstance(pos, Tensor) else (None, int(pos))
+    if pos_dev is not None and (pos_dev.dtype != torch.int32 or not pos_dev.is_cuda):
+        raise CdssmError("a tensor position must be an int32 CUDA tensor")
+    with torch.cuda.device(q.device):
+        check(_lib.lib().cdssm_b200_decode_step_reference(
+            _p(state["local"]), _p(state["correction"]), _p(state["carry"]), _p(state["decay"]), _p(q), _p(k), _p(v),
+            _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps,
+            shortcut_scale, B, H, D, N, int(chunk_size), pos_i, _p(pos_dev), _dtype_code(q), _stream()),
+            "decode_step_reference")
     return y
 
 

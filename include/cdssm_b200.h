@@ -282,6 +282,25 @@ CDSSM_API int cdssm_b200_decode_step_at(float* state, const void* q, const void*
                                         float adt_eps, float shortcut_scale, int B, int H, int D, int N,
                                         const int* pos_dev, int dtype, void* stream);
 
+/* One-token decode step that reproduces the reference's CHUNKED scan (whose outputs beyond the first chunk are
+ * not those of the plain recurrence): the state per (batch, head) is the local state (zero at every chunk
+ * start), the correction (starts from the bf16-rounded carry; erased and rotated, never injected; read BEFORE
+ * its step, cdssm/csrc/kernels/exact_correction.cu:89-150), the carry (decay-only recurrence over chunks,
+ * inter_chunk_scan.cu:52-84) and the chunk's cumulative decay.  local_state, correction, carry: (B,H,N,D)
+ * float32; chunk_decay: (B,H,N) float32 (re/im interleaved), all updated in place.  pos (or *pos_dev if not NULL)
+ * is the token's position counted from the start of the sequence; chunks are C tokens.  Starting from
+ * local_state = 0, correction = carry rounded to the storage type, chunk_decay = (1, 0) at a chunk boundary, T
+ * steps give the y of cdssm_b200_scan_fused_fwd over the same T tokens with that carry as h0.
+ * The reference has no decode step; this is what its full re-forward per token
+ * (cdssm/inference/predict.py:53-67) computes for the newest position of the scan. */
+CDSSM_API int cdssm_b200_decode_step_reference(float* local_state, float* correction, float* carry,
+                                               float* chunk_decay, const void* q, const void* k, const void* v,
+                                               const void* gate_raw, const float* log_dt_scale,
+                                               const float* rope_freqs, void* y, float gating_c, float omega_thresh,
+                                               float adt_delta, float adt_smoothness, float adt_eps,
+                                               float shortcut_scale, int B, int H, int D, int N, int C, int pos,
+                                               const int* pos_dev, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

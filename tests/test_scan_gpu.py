@@ -231,3 +231,47 @@ def test_exact_prefill_feeds_decode_beyond_one_chunk(ops, orc):
                           *const_args(inp["consts"]), H, N, t) for t in range(T0, T0 + T1)]
     y = torch.cat([y0, torch.stack(ys, 1)], 1)
     assert rel_err(to_np(y), wy) <= FP32_TOL
+
+
+@pytest.mark.parametrize("dtype,mask,tol", [(torch.float32, 0, FP32_TOL), (torch.bfloat16, 13, BF16_TOL / 2)])
+@pytest.mark.parametrize("B,H,D,N,C,T", [(2, 3, 64, 2, 64, 3 * 64 + 7), (1, 2, 64, 4, 64, 130), (1, 4, 128, 2, 128, 300),
+                                         (1, 2, 40, 2, 24, 60)])
+def test_reference_decode_steps_equal_the_chunked_scan(ops, orc, dtype, mask, tol, B, H, D, N, C, T):
+    """T reference-compatible decode steps from the start of a sequence reproduce the reference's chunked scan
+    over T tokens - beyond the first chunk too, where the plain recurrence (decode_step) does not."""
+    inp = orc.make_inputs(B, H, T, D, N=N, seed=T + D, bf16=mask != 0, context_length=512)
+    wy, _ = oracle_scan(orc, inp, N, C, mask, shortcut_scale=0.3)
+    d = lambda x: to_dev(x, dtype)
+    lds, rf = to_dev(inp["log_dt_scale"], torch.float32), to_dev(inp["rope_freqs"], torch.float32)
+    q, k, v, g = d(inp["q"]), d(inp["k"]), d(inp["v"]), d(inp["gate_raw"])
+    st = ops.reference_decode_state(torch.zeros(B, H, N, D, device="cuda"), dtype)
+    ys = [ops.decode_step_reference(st, q[:, t], k[:, t], v[:, t], g[:, t], lds, rf, *const_args(inp["consts"]), H, N, C,
+                                    t, shortcut_scale=0.3) for t in range(T)]
+    y = torch.stack(ys, 1)
+    assert rel_err(to_np(y), wy) <= tol
+    yf, _ = run_fused(ops, inp, dtype, N, C, shortcut_scale=0.3)
+    assert rel_err(to_np(y), to_np(yf)) <= tol
+    if T > C:   # the plain recurrence really is something else there
+        wrec, _ = orc.scan_recurrent(inp["q"], inp["k"], inp["v"], inp["gate_raw"], inp["log_dt_scale"],
+                                     inp["rope_freqs"], inp["consts"], N, shortcut_scale=0.3, round_bf16=mask)
+        assert rel_err(wrec, wy) > 10 * tol
+
+
+def test_reference_decode_continues_a_chunk_aligned_prefill(ops, orc):
+    B, H, D, N, C, L0, T = 2, 4, 64, 2, 64, 128, 64 + 9
+    inp = orc.make_inputs(B, H, L0 + T, D, N=N, seed=5, bf16=True, context_length=512)
+    full, _ = run_fused(ops, inp, torch.bfloat16, N, C)
+    head = {k: (v[:, :L0] if getattr(v, "ndim", 0) >= 3 else v) for k, v in inp.items()}
+    _, carry = run_fused(ops, head, torch.bfloat16, N, C)
+    st = ops.reference_decode_state(carry, torch.bfloat16)
+    d = lambda x: to_dev(x, torch.bfloat16)
+    lds, rf = to_dev(inp["log_dt_scale"], torch.float32), to_dev(inp["rope_freqs"], torch.float32)
+    q, k, v, g = d(inp["q"]), d(inp["k"]), d(inp["v"]), d(inp["gate_raw"])
+    pos = torch.tensor([L0], dtype=torch.int32, device="cuda")      # the graph-replayable form of the position
+    ys = []
+    for t in range(L0, L0 + T):
+        ys.append(ops.decode_step_reference(st, q[:, t], k[:, t], v[:, t], g[:, t], lds, rf,
+                                            *const_args(inp["consts"]), H, N, C, pos))
+        pos += 1
+    y = torch.stack(ys, 1)
+    assert rel_err(to_np(y), to_np(full[:, L0:])) <= BF16_TOL / 2
