@@ -2,7 +2,7 @@
 //
 // These keep the reference's operator boundaries (and therefore its HBM traffic: the
 // (B,L,H,N,D) tensors are materialised) so that cdssm/models/ssd.py and block.py can run on
-// them unchanged.  The measured path is the fused one in scan_fused.cu; these exist for the
+// them unchanged.  The measured path is the fused one (scan_wa.cu, scan_simt.cu); these exist for the
 // strict drop-in and as building blocks of the parity tests.
 //
 // Thread mappings differ from the reference's (one block of D threads per (chunk, head) with

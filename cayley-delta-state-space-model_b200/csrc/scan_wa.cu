@@ -5,21 +5,24 @@
 //
 // A thread block owns the same chunk of FOUR heads and walks it in 32-token sub-blocks; UMMA tile row
 // 32 j + t is token t of head j's sub-block and compute warp j owns head j.  Per sub-block:
-//   G_j = K_j K_j^T, P_j = Q_j K_j^T    : the 32 x 32 diagonal blocks only - one UMMA (N = 64) per pair of heads
-//                                         with every output lane but the pair's 64 masked off.  They depend
-//                                         on nothing but the tiles, so the producer warp issues them as soon
-//                                         as a tile has landed, a step ahead of the compute warps, into one
-//                                         of two tensor-memory slots.
+//   G = K K^T, P = Q K^T                : one full-width UMMA (M = N = 128) per 16-column k-step; head j reads its
+//                                         own 32 x 32 diagonal block (lanes 32 j.., columns 32 j..).  The blocks
+//                                         depend on nothing but the tiles, so the producer warp issues them as soon
+//                                         as a tile has landed, a step ahead of the compute warps.
 //   kappa, rho = K S^T, Q S^T           : products with the running states (local state z, correction r;
 //                                         bf16 hi + lo columns), warp-level mma.sync on the warp's own 32
 //                                         tile rows (ldmatrix straight from the swizzled TMA tile) with the
-//                                         state held in the warp's registers in fragment layout.
+//                                         state held in the warp's registers in fragment layout.  |q_t|^2 comes
+//                                         from the same Q fragments (diagonal of Q Q^T).
 //   solve / read-out                    : unit-lower-triangular 32 x 32 systems by substitution through
 //                                         warp shuffles, rows from tcgen05.ld (thread = token = TMEM lane).
 //   S <- W_31 S + K^T Omega             : warp-level mma.sync again (ldmatrix.trans of the same K rows),
 //                                         accumulating onto the decayed state registers.
 // A step of a warp therefore contains no hand-off to another warp: the only barriers are "tile landed",
-// "Gram blocks done" and the releases of tile and tensor-memory slots back to the producer.
+// "Gram blocks done" and the releases of tiles and tensor memory back to the producer.  Buffers: two K tiles
+// (the update at the end of a step still reads the tile while the next one lands), one Q tile (handed back
+// right after rho and |q|, a fifth into the step), one set of tensor-memory columns (handed back once the
+// rows are in registers).
 //
 // Reference semantics (intra_chunk_scan.cu:100-195, exact_correction.cu:89-150): z starts at zero at the
 // chunk start, r starts from the chunk's carry (bf16, from the carry pass), the correction is read before
@@ -117,7 +120,7 @@ __device__ __forceinline__ size_t rec_index(const Args& a, int steps, int b, int
 
 // ------------------------------------------------------------------------------------------
 // Producer warp: TMA loads and the Gram UMMAs, strictly in step order.  The block's work is a flat sequence
-// of sub-block steps g; step g uses K slot g & 1, the single Q buffer and tensor-memory slot g & 1.
+// of sub-block steps g; step g uses K slot g & 1, the single Q buffer and the single set of tensor-memory columns.
 // ------------------------------------------------------------------------------------------
 template <int kD, bool kOutput>
 __device__ __forceinline__ void producer(Smem<kD, kOutput>& sm, const CUtensorMap* tmK, const CUtensorMap* tmQ,

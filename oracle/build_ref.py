@@ -8,7 +8,8 @@ cannot load on a B200, so the same sources are compiled here for sm_100 with the
 reference's other flags (`-O3 --use_fast_math`).  The result is a torch extension
 module `cdssm_ref_C` exposing the twelve `*_cuda` functions of cdssm/csrc/binding.cpp:130-202.
 
-Usage:  python oracle/build_ref.py [reference_root]   (default: $CDSSM_REFERENCE_ROOT or the mounted checkout)
+Usage:  python oracle/build_ref.py [reference_root]   (default: $CDSSM_REFERENCE_ROOT, else a checkout named
+`reference` beside this repository)
 The sources are never copied into this repository; only the built `.so` lands in
 oracle/_ref/ (git-ignored).
 """
@@ -26,8 +27,19 @@ def ref_so_path():
     return os.path.join(OUT, "cdssm_ref_C.so")
 
 
+def default_reference_root():
+    """$CDSSM_REFERENCE_ROOT, else a checkout named ``reference`` beside this repository, else None."""
+    env = os.environ.get("CDSSM_REFERENCE_ROOT")
+    if env:
+        return env
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return beside if os.path.isdir(beside) else None
+
+
 def build(reference_root=None, verbose=False):
-    reference_root = reference_root or os.environ.get("CDSSM_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+    reference_root = reference_root or default_reference_root()
+    if not reference_root:
+        raise FileNotFoundError("no reference checkout: set CDSSM_REFERENCE_ROOT")
     csrc = os.path.join(reference_root, "cdssm", "csrc")
     if not os.path.isdir(csrc):
         raise FileNotFoundError(f"reference sources not found under {reference_root}")
