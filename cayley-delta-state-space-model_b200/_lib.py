@@ -27,6 +27,8 @@ SIGNATURES = {
     "cdssm_b200_version": (_I, []),
     "cdssm_b200_last_cuda_error": (_I, []),
     "cdssm_b200_dynamics_fwd": (_I, [_P] * 7 + [_F] * 5 + [_I] * 6 + [_P]),
+    "cdssm_b200_dynamics_bwd": (_I, [_P] * 9 + [_F] * 5 + [_I] * 6 + [_P]),
+    "cdssm_b200_normalize_kq_bwd": (_I, [_P] * 6 + [_c_int64, _I, _I, _P]),
     "cdssm_b200_normalize_kq_fwd": (_I, [_P] * 4 + [_c_int64, _I, _I, _P]),
     "cdssm_b200_intra_chunk_scan_fwd": (_I, [_P] * 6 + [_I] * 6 + [_P]),
     "cdssm_b200_inter_chunk_scan_fwd": (_I, [_P] * 3 + [_I] * 6 + [_P]),

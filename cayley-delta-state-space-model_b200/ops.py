@@ -59,7 +59,8 @@ def _p(t):
 
 
 def _no_backward(*_):
-    raise NotImplementedError("this build implements the forward (prefill/decode) path only")
+    raise NotImplementedError("backward is implemented for DynamicsFusedFn and NormalizeKQFn only; the scan-side "
+                              "operators run forward (prefill / decode)")
 
 
 class CUDAConv1dSiLUOp(Function):
@@ -105,9 +106,28 @@ class DynamicsFusedFn(Function):
                 _p(g), _p(lds), _p(rf), _p(A), _p(vp), _p(beta), _p(selc), gating_c, omega_thresh,
                 adt_delta, adt_smoothness, adt_eps, B, L, H, N, 0, _dtype_code(g), _stream()),
                 "dynamics_fwd")
+        ctx.save_for_backward(g, lds, rf)
+        ctx.consts = (gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps)
+        ctx.dims = (B, L, H, N)
+        ctx.lds_dtype = log_dt_scale.dtype
         return A, vp, beta, selc
 
-    backward = staticmethod(_no_backward)
+    @staticmethod
+    def backward(ctx, grad_A_bar, grad_vp_scale, grad_beta, grad_sel_C):
+        """(grad_gate_raw, grad_log_dt_scale, None x 8), as cdssm/ops.py:68-81 (dynamics_fused.cu:145-387)."""
+        g, lds, rf = ctx.saved_tensors
+        B, L, H, N = ctx.dims
+        z = lambda t, shape: (torch.zeros(shape, dtype=g.dtype, device=g.device) if t is None
+                              else _prep(t.to(g.dtype), name="upstream gradient"))
+        gA, gvp = z(grad_A_bar, (B, L, H, N)), z(grad_vp_scale, (B, L, H, N // 2))
+        gb, gc = z(grad_beta, (B, L, H)), z(grad_sel_C, (B, L, H))
+        gg = torch.empty_like(g)
+        glds = torch.empty(H, dtype=torch.float32, device=g.device)
+        with torch.cuda.device(g.device):
+            check(_lib.lib().cdssm_b200_dynamics_bwd(
+                _p(gA), _p(gvp), _p(gb), _p(gc), _p(g), _p(lds), _p(rf), _p(gg), _p(glds), *ctx.consts, B, L, H, N, 0,
+                _dtype_code(g), _stream()), "dynamics_bwd")
+        return (gg, glds.to(ctx.lds_dtype)) + (None,) * 8
 
 
 class NormalizeKQFn(Function):
@@ -125,9 +145,22 @@ class NormalizeKQFn(Function):
             check(_lib.lib().cdssm_b200_normalize_kq_fwd(_p(K), _p(Q), _p(Ko), _p(Qo),
                                                          K.numel() // D, D, _dtype_code(K), _stream()),
                   "normalize_kq_fwd")
+        ctx.save_for_backward(K, Q)
         return Ko, Qo
 
-    backward = staticmethod(_no_backward)
+    @staticmethod
+    def backward(ctx, grad_K_out, grad_Q_out):
+        """(grad_K, grad_Q), as cdssm/ops.py:93-97 (normalize_kq.cu:89-163)."""
+        K, Q = ctx.saved_tensors
+        D = K.shape[-1]
+        z = lambda t: torch.zeros_like(K) if t is None else _prep(t.to(K.dtype), name="upstream gradient")
+        gKo, gQo = z(grad_K_out), z(grad_Q_out)
+        gK, gQ = torch.empty_like(K), torch.empty_like(Q)
+        with torch.cuda.device(K.device):
+            check(_lib.lib().cdssm_b200_normalize_kq_bwd(_p(gKo), _p(gQo), _p(K), _p(Q), _p(gK), _p(gQ),
+                                                         K.numel() // D, D, _dtype_code(K), _stream()),
+                  "normalize_kq_bwd")
+        return gK, gQ
 
 
 class IntraChunkScanFn(Function):

@@ -58,6 +58,21 @@ CDSSM_API int cdssm_b200_dynamics_fwd(const void* gate_raw, const float* log_dt_
 CDSSM_API int cdssm_b200_normalize_kq_fwd(const void* K, const void* Q, void* K_out, void* Q_out,
                                 int64_t rows, int D, int dtype, void* stream);
 
+/* Backward of cdssm_b200_dynamics_fwd: upstream gradients of A_bar (B,L,H,N), vp_scale (B,L,H,N/2), beta, sel_C
+ * (B,L,H) -> grad_gate_raw (B,L,(N+5)*H) in the storage type and grad_log_dt_scale (H) float32 (zeroed and
+ * accumulated by the call; the accumulation order over tokens is not fixed).
+ * Replaces dynamics_fused_bwd_cuda, cdssm/csrc/kernels/dynamics_fused.cu:145-387 (cdssm/ops.py:68-81). */
+CDSSM_API int cdssm_b200_dynamics_bwd(const void* grad_A_bar, const void* grad_vp_scale, const void* grad_beta,
+                            const void* grad_sel_C, const void* gate_raw, const float* log_dt_scale,
+                            const float* rope_freqs, void* grad_gate_raw, float* grad_log_dt_scale,
+                            float gating_c, float omega_thresh, float adt_delta, float adt_smoothness,
+                            float adt_eps, int B, int L, int H, int N, int pos0, int dtype, void* stream);
+
+/* Backward of cdssm_b200_normalize_kq_fwd: grad_x = n (g - x_hat (g . x_hat)), n = rsqrt(|x|^2 + 1e-6).
+ * Replaces normalize_kq_bwd_cuda, cdssm/csrc/kernels/normalize_kq.cu:89-163 (cdssm/ops.py:93-97). */
+CDSSM_API int cdssm_b200_normalize_kq_bwd(const void* grad_K_out, const void* grad_Q_out, const void* K, const void* Q,
+                                void* grad_K, void* grad_Q, int64_t rows, int D, int dtype, void* stream);
+
 /* Intra-chunk delta-rule scan from a zero state.  A (BNC,C,H,N), K (BNC,C,H,D), V (BNC,C,H,N),
  * beta (BNC,C,H) -> local_h (BNC,C,H,N,D), cum_A (BNC,C,H,N).
  * Replaces intra_chunk_scan_fwd_cuda, cdssm/csrc/kernels/intra_chunk_scan.cu:560-609

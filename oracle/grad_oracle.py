@@ -1,0 +1,151 @@
+"""Gradient oracle for the two memory-bound operators (float64 numpy).
+
+TEST INFRASTRUCTURE ONLY.  ``dynamics_forward`` restates the forward of dynamics_fused.cu:64-139 without any
+rounding; ``dynamics_backward`` restates the chain of dynamics_fused.cu:187-386 (gate sigmoids, per-pair variance
+scale / recurrence gate / Cayley map, adaptive time step, log_dt_scale); ``normalize_backward`` restates
+normalize_kq.cu:118-160.  tests/test_grad_oracle.py checks both backward functions against central finite differences
+of the forward functions, so a kernel that agrees with them agrees with the derivative of the forward.
+"""
+import numpy as np
+
+EPS = 1e-6   # common.cuh:142
+
+
+def _sig(x):
+    return 1.0 / (1.0 + np.exp(-np.clip(x, -700.0, 700.0)))
+
+
+def _sp(x):
+    return np.where(x > 20.0, x, np.log1p(np.exp(np.minimum(x, 20.0))))
+
+
+def _split(gate_raw, H, N):
+    g = np.asarray(gate_raw, np.float64)
+    B, L, _ = g.shape
+    return g.reshape(B, L, N + 5, H)          # segment-major, head-minor (dynamics_fused.cu:60-81)
+
+
+def _shared(g, lds, rf, c, N, pos0):
+    """Per (b,l,h) quantities shared by the pairs.  Returns a dict of arrays (B,L,H)."""
+    B, L, _, H = g.shape
+    NH = N // 2
+    pos = (np.arange(L, dtype=np.float64) + pos0)[None, :, None]
+    rot = pos * np.asarray(rf, np.float64)[None, None, :]
+    selB, selC, seldt, beta_raw, r_raw = (g[:, :, N + i] for i in range(5))
+    a0_raw, w0 = g[:, :, 0], g[:, :, NH] + rot
+    alpha0, w0a = _sp(a0_raw), np.abs(w0)
+    s = _sp(np.asarray(lds, np.float64))[None, None, :]
+    cf = alpha0 + w0a + c["adt_eps"]
+    dt_raw = s / cf
+    am = alpha0 + c["adt_eps"]
+    dt_max = (2.0 - c["adt_delta"]) / am
+    blend = _sig((c["omega_thresh"] - w0a) / c["adt_smoothness"])
+    dt = blend * np.minimum(dt_raw, dt_max) + (1.0 - blend) * dt_raw + _sp(seldt)
+    return dict(rot=rot, selB=selB, selC=selC, seldt=seldt, beta_raw=beta_raw, r_raw=r_raw, a0_raw=a0_raw, w0=w0,
+                alpha0=alpha0, w0a=w0a, s=s, cf=cf, dt_raw=dt_raw, am=am, dt_max=dt_max, blend=blend, dt=dt,
+                r=_sig(r_raw))
+
+
+def dynamics_forward(gate_raw, log_dt_scale, rope_freqs, consts, H, N, pos0=0):
+    """-> A_bar (B,L,H,N), vp_scale (B,L,H,N/2), beta (B,L,H), sel_C (B,L,H), float64."""
+    g = _split(gate_raw, H, N)
+    B, L = g.shape[:2]
+    NH = N // 2
+    sh = _shared(g, log_dt_scale, rope_freqs, consts, N, pos0)
+    cr = consts["gating_c"] * sh["r"]
+    A = np.empty((B, L, H, N))
+    vp = np.empty((B, L, H, NH))
+    for j in range(NH):
+        alpha = np.maximum(_sp(g[:, :, j]), 0.0)
+        omega = g[:, :, NH + j] + sh["rot"]
+        tau = 0.5 * sh["dt"]
+        ta, tw = tau * alpha, tau * omega
+        den = (1 + ta) ** 2 + tw ** 2 + EPS
+        mu_re = ((1 - ta) * (1 + ta) - tw ** 2) / den
+        mu_im = (tw * (1 + ta) + (1 - ta) * tw) / den
+        e = np.maximum(((1 - ta) ** 2 + tw ** 2) / den, 1e-8)
+        scale = e ** ((cr - 1.0) / 2.0)
+        A[..., 2 * j], A[..., 2 * j + 1] = mu_re * scale, -mu_im * scale
+        vp[..., j] = np.minimum(np.sqrt(np.maximum(1.0 - e ** cr, EPS)), 1.0)
+    return A, vp, _sig(sh["beta_raw"]) * _sig(sh["selB"]), _sig(sh["selC"])
+
+
+def dynamics_backward(gA, gvp, gbeta, gselc, gate_raw, log_dt_scale, rope_freqs, consts, H, N, pos0=0):
+    """-> grad_gate_raw (B,L,(N+5)H), grad_log_dt_scale (H), float64."""
+    g = _split(gate_raw, H, N)
+    B, L = g.shape[:2]
+    NH = N // 2
+    c = consts
+    sh = _shared(g, log_dt_scale, rope_freqs, c, N, pos0)
+    gA, gvp = np.asarray(gA, np.float64), np.asarray(gvp, np.float64)
+    gbeta, gselc = np.asarray(gbeta, np.float64), np.asarray(gselc, np.float64)
+    out = np.zeros_like(g)
+    r, dt = sh["r"], sh["dt"]
+    cr = c["gating_c"] * r
+    expo = (cr - 1.0) / 2.0
+    g_dt = np.zeros((B, L, H))
+    g_r = np.zeros((B, L, H))
+    for j in range(NH):
+        a_raw = g[:, :, j]
+        alpha = np.maximum(_sp(a_raw), 0.0)
+        omega = g[:, :, NH + j] + sh["rot"]
+        tau = 0.5 * dt
+        ta, tw = tau * alpha, tau * omega
+        opa, oma = 1 + ta, 1 - ta
+        det = opa ** 2 + tw ** 2 + EPS
+        num_re = oma * opa - tw ** 2
+        mu_re, mu_im = num_re / det, 2 * tw / det
+        e_raw = (oma ** 2 + tw ** 2) / det
+        e = np.maximum(e_raw, 1e-8)
+        free = e_raw > 1e-8
+        scale, eff = e ** expo, e ** cr
+        vp2 = 1.0 - eff
+        # variance-preserving scale (dynamics_fused.cu:258-262)
+        d_eff = np.where((vp2 > EPS) & (vp2 < 1.0), gvp[..., j] * (-0.5 / np.sqrt(np.maximum(vp2, EPS))), 0.0)
+        # recurrence gate exponent (:264-282)
+        d_scale = gA[..., 2 * j] * mu_re + gA[..., 2 * j + 1] * (-mu_im)
+        d_e = np.where(free, d_eff * cr * e ** (cr - 1.0) + d_scale * expo * e ** (expo - 1.0), 0.0)
+        g_r += d_eff * c["gating_c"] * np.log(e) * eff + d_scale * (c["gating_c"] / 2.0) * np.log(e) * scale
+        # Cayley map (:288-340): e = num / det, mu = (num_re, 2 tw) / det, stored conjugated
+        gm_re, gm_im = gA[..., 2 * j] * scale, -gA[..., 2 * j + 1] * scale
+        d_ta = d_e * (-2 * oma) / det - d_e * e_raw * 2 * opa / det
+        d_tw = d_e * 2 * tw / det - d_e * e_raw * 2 * tw / det
+        d_ta += gm_re * (-2 * ta * det - num_re * 2 * opa) / det ** 2 + gm_im * (-2 * tw * 2 * opa) / det ** 2
+        d_tw += gm_re * (-2 * tw * det - num_re * 2 * tw) / det ** 2 + gm_im * (2 * det - 4 * tw * tw) / det ** 2
+        out[:, :, j] += d_ta * tau * _sig(a_raw)
+        out[:, :, NH + j] += d_tw * tau
+        g_dt += 0.5 * (d_ta * alpha + d_tw * omega)
+    # adaptive time step (:348-372)
+    capped = sh["dt_raw"] > sh["dt_max"]
+    blend = sh["blend"]
+    g_raw = g_dt * np.where(capped, 1.0 - blend, 1.0)
+    g_max = g_dt * np.where(capped, blend, 0.0)
+    g_blend = g_dt * (np.minimum(sh["dt_raw"], sh["dt_max"]) - sh["dt_raw"])
+    g_s = g_raw / sh["cf"]
+    g_cf = -g_raw * sh["s"] / sh["cf"] ** 2
+    g_w0a = g_cf - g_blend * blend * (1 - blend) / c["adt_smoothness"]
+    g_alpha0 = g_cf - g_max * (2.0 - c["adt_delta"]) / sh["am"] ** 2
+    out[:, :, 0] += g_alpha0 * _sig(sh["a0_raw"])
+    out[:, :, NH] += g_w0a * np.where(sh["w0"] >= 0, 1.0, -1.0)
+    # gates (:208-217, :374-383)
+    sb, sbe, sc = _sig(sh["selB"]), _sig(sh["beta_raw"]), _sig(sh["selC"])
+    out[:, :, N] = gbeta * sbe * sb * (1 - sb)
+    out[:, :, N + 1] = gselc * sc * (1 - sc)
+    out[:, :, N + 2] = g_dt * _sig(sh["seldt"])
+    out[:, :, N + 3] = gbeta * sb * sbe * (1 - sbe)
+    out[:, :, N + 4] = g_r * r * (1 - r)
+    glds = (g_s * _sig(np.asarray(log_dt_scale, np.float64))[None, None, :]).sum((0, 1))
+    return out.reshape(B, L, (N + 5) * H), glds
+
+
+def normalize_forward(x):
+    x = np.asarray(x, np.float64)
+    return x / np.sqrt((x ** 2).sum(-1, keepdims=True) + EPS)
+
+
+def normalize_backward(g_out, x):
+    """normalize_kq.cu:118-160: grad_in = (g - x_hat (g . x_hat)) * inv_norm."""
+    x, g_out = np.asarray(x, np.float64), np.asarray(g_out, np.float64)
+    inv = 1.0 / np.sqrt((x ** 2).sum(-1, keepdims=True) + EPS)
+    xh = x * inv
+    return (g_out - xh * (g_out * xh).sum(-1, keepdims=True)) * inv

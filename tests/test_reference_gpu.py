@@ -69,3 +69,29 @@ def test_tensor_core_passes_against_reference_kernels(ops, orc, ref, B, H, L, D)
     y, _ = ops.scan_fused(q, k, v, gate, lds, rf, *consts, H, N, C, shortcut_scale=0.5, flags=ops.TENSOR_CORE_WA)
     assert ops.scan_fused_status() == 0
     assert rel_err(to_np(y), to_np(want)) <= BF16_TOL
+
+
+def test_backward_kernels_against_reference_backward_kernels(ops, orc, ref):
+    """dynamics and normalisation backward against the reference's own backward kernels on the same bf16 data."""
+    B, H, L, N, D = 2, 4, 96, 2, 64
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=7, bf16=True, context_length=256)
+    bf = lambda a: torch.from_numpy(a).cuda().bfloat16()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda").bfloat16()
+    gate, lds = bf(inp["gate_raw"]), torch.from_numpy(inp["log_dt_scale"]).cuda()
+    rf = torch.from_numpy(inp["rope_freqs"]).cuda()
+    consts = const_args(inp["consts"])
+    ups = [rn(B, L, H, N), rn(B, L, H, N // 2), rn(B, L, H), rn(B, L, H)]
+    want_g, want_l = ref.dynamics_fused_bwd_cuda(*ups, gate, lds, rf, *consts, H, N)
+    gt = gate.clone().requires_grad_(True)
+    lt = lds.clone().requires_grad_(True)
+    outs = ops.DynamicsFusedFn.apply(gt, lt, rf, *consts, H, N)
+    torch.autograd.backward(outs, ups)
+    assert rel_err(to_np(gt.grad), to_np(want_g)) <= BF16_TOL
+    assert rel_err(to_np(lt.grad), to_np(want_l)) <= BF16_TOL
+    K, Q, gK, gQ = (rn(B, L, H, D) for _ in range(4))
+    wK, wQ = ref.normalize_kq_bwd_cuda(gK, gQ, K, Q)
+    kt, qt = K.clone().requires_grad_(True), Q.clone().requires_grad_(True)
+    torch.autograd.backward(ops.NormalizeKQFn.apply(kt, qt), [gK, gQ])
+    assert rel_err(to_np(kt.grad), to_np(wK)) <= BF16_TOL / 2
+    assert rel_err(to_np(qt.grad), to_np(wQ)) <= BF16_TOL / 2
