@@ -27,6 +27,10 @@ SIGNATURES = {
     "cdssm_b200_version": (_I, []),
     "cdssm_b200_last_cuda_error": (_I, []),
     "cdssm_b200_dynamics_fwd": (_I, [_P] * 7 + [_F] * 5 + [_I] * 6 + [_P]),
+    "cdssm_b200_intra_chunk_scan_bwd": (_I, [_P] * 12 + [_I] * 6 + [_P]),
+    "cdssm_b200_exact_correction_bwd": (_I, [_P] * 9 + [_I] * 8 + [_P]),
+    "cdssm_b200_inter_chunk_scan_bwd": (_I, [_P] * 5 + [_I] * 6 + [_P]),
+    "cdssm_b200_conv1d_silu_bwd": (_I, [_P] * 7 + [_I] * 4 + [_P]),
     "cdssm_b200_dynamics_bwd": (_I, [_P] * 9 + [_F] * 5 + [_I] * 6 + [_P]),
     "cdssm_b200_normalize_kq_bwd": (_I, [_P] * 6 + [_c_int64, _I, _I, _P]),
     "cdssm_b200_normalize_kq_fwd": (_I, [_P] * 4 + [_c_int64, _I, _I, _P]),

@@ -58,11 +58,6 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
-def _no_backward(*_):
-    raise NotImplementedError("backward is implemented for DynamicsFusedFn and NormalizeKQFn only; the scan-side "
-                              "operators run forward (prefill / decode)")
-
-
 class CUDAConv1dSiLUOp(Function):
     """Causal depthwise conv (kernel 4) + bias + SiLU; cdssm/ops.py:13-28."""
 
@@ -78,9 +73,24 @@ class CUDAConv1dSiLUOp(Function):
         with torch.cuda.device(x.device):
             check(_lib.lib().cdssm_b200_conv1d_silu_fwd(_p(x), _p(w), _p(b), _p(out), B, L, Dm,
                                                         _dtype_code(x), _stream()), "conv1d_silu_fwd")
+        ctx.save_for_backward(x, w, b)
+        ctx.param_meta = (weight.shape, weight.dtype, bias.dtype)
         return out
 
-    backward = staticmethod(_no_backward)
+    @staticmethod
+    def backward(ctx, grad_out):
+        """(grad_x, grad_weight, grad_bias), as cdssm/ops.py:22-28 (conv1d_silu.cu:94-219)."""
+        x, w, b = ctx.saved_tensors
+        B, L, Dm = x.shape
+        go = _prep(grad_out.to(x.dtype), name="grad_out")
+        gx = torch.empty_like(x)
+        gw = torch.empty(Dm, 4, dtype=torch.float32, device=x.device)
+        gb = torch.empty(Dm, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            check(_lib.lib().cdssm_b200_conv1d_silu_bwd(_p(go), _p(x), _p(w), _p(b), _p(gx), _p(gw), _p(gb), B, L, Dm,
+                                                        _dtype_code(x), _stream()), "conv1d_silu_bwd")
+        wshape, wdt, bdt = ctx.param_meta
+        return gx, gw.reshape(wshape).to(wdt), gb.to(bdt)
 
 
 class DynamicsFusedFn(Function):
@@ -180,9 +190,26 @@ class IntraChunkScanFn(Function):
             check(_lib.lib().cdssm_b200_intra_chunk_scan_fwd(
                 _p(A), _p(K), _p(V), _p(be), _p(local_h), _p(cum_A), BNC, C, H, D, N,
                 _dtype_code(K), _stream()), "intra_chunk_scan_fwd")
+        ctx.save_for_backward(A, K, V, be, local_h, cum_A)
+        ctx.state_dim = N
         return local_h, cum_A
 
-    backward = staticmethod(_no_backward)
+    @staticmethod
+    def backward(ctx, grad_local_h, grad_cum_A):
+        """(grad_A, grad_K, grad_V, grad_beta, None), as cdssm/ops.py:123-135 (intra_chunk_scan.cu:215-553)."""
+        A, K, V, be, local_h, cum_A = ctx.saved_tensors
+        BNC, C, H, D = K.shape
+        N = ctx.state_dim
+        glh = torch.zeros_like(local_h) if grad_local_h is None else _prep(grad_local_h.to(K.dtype), name="grad_local_h")
+        gca = torch.zeros_like(cum_A) if grad_cum_A is None else _prep(grad_cum_A.to(K.dtype), name="grad_cum_A")
+        gA, gV = torch.empty_like(A), torch.empty_like(V)
+        gK = torch.empty(BNC, C, H, D, dtype=torch.float32, device=K.device)
+        gB = torch.empty(BNC, C, H, dtype=torch.float32, device=K.device)
+        with torch.cuda.device(K.device):
+            check(_lib.lib().cdssm_b200_intra_chunk_scan_bwd(
+                _p(glh), _p(gca), _p(A), _p(K), _p(V), _p(be), _p(local_h), _p(cum_A), _p(gA), _p(gK), _p(gV), _p(gB),
+                BNC, C, H, D, N, _dtype_code(K), _stream()), "intra_chunk_scan_bwd")
+        return gA, gK.to(K.dtype), gV, gB.to(be.dtype), None
 
 
 class InterChunkScanFn(Function):
@@ -198,9 +225,29 @@ class InterChunkScanFn(Function):
             check(_lib.lib().cdssm_b200_inter_chunk_scan_fwd(_p(a), _p(f), _p(out), B, NC, H, D,
                                                              int(state_dim), _dtype_code(f), _stream()),
                   "inter_chunk_scan_fwd")
+        ctx.save_for_backward(a, out)
+        ctx.state_dim = int(state_dim)
         return out
 
-    backward = staticmethod(_no_backward)
+    @staticmethod
+    def backward(ctx, grad_chunk_states):
+        """(grad_total_A, grad_final_local_h, None), as cdssm/ops.py:157-163 (inter_chunk_scan.cu:89-196)."""
+        a, states = ctx.saved_tensors
+        B, NC, H, N, D = states.shape
+        g = _prep(grad_chunk_states.to(states.dtype), name="grad_chunk_states")
+        gA, gH = torch.empty_like(a), torch.empty_like(states)
+        with torch.cuda.device(states.device):
+            check(_lib.lib().cdssm_b200_inter_chunk_scan_bwd(_p(g), _p(a), _p(states), _p(gA), _p(gH), B, NC, H, D,
+                                                             ctx.state_dim, _dtype_code(states), _stream()),
+                  "inter_chunk_scan_bwd")
+        return gA, gH, None
+
+
+# The reference's correction backward kernel adds the upstream gradient of corrections[t] BEFORE it walks step t
+# back (exact_correction.cu:219-223), although the forward stores corrections[t] before the step (:90-94), and its
+# grad_beta is head_dim times too large (:347-359): its gradient is not the derivative of its forward.  The drop-in default reproduces the reference (what its training
+# runs with); set this to True for the true derivative.
+EXACT_CORRECTION_TRUE_GRADIENT = False
 
 
 class ExactCorrectionFn(Function):
@@ -220,9 +267,27 @@ class ExactCorrectionFn(Function):
             check(_lib.lib().cdssm_b200_exact_correction_fwd(
                 _p(A), _p(K), _p(be), _p(cs), _p(out), B, NC, C, H, D, N, _dtype_code(K), _stream()),
                 "exact_correction_fwd")
+        ctx.save_for_backward(A, K, be, out)
+        ctx.state_dim = N
         return out
 
-    backward = staticmethod(_no_backward)
+    @staticmethod
+    def backward(ctx, grad_corrections):
+        """(grad_A, grad_K, grad_beta, grad_chunk_states, None), as cdssm/ops.py:188-195
+        (exact_correction.cu:169-383)."""
+        A, K, be, corr = ctx.saved_tensors
+        B, NC, C, H, D = K.shape
+        N = ctx.state_dim
+        g = _prep(grad_corrections.to(K.dtype), name="grad_corrections")
+        gA = torch.empty_like(A)
+        gK = torch.empty(B, NC, C, H, D, dtype=torch.float32, device=K.device)
+        gB = torch.empty(B, NC, C, H, dtype=torch.float32, device=K.device)
+        gS = torch.empty(B, NC, H, N, D, dtype=K.dtype, device=K.device)
+        with torch.cuda.device(K.device):
+            check(_lib.lib().cdssm_b200_exact_correction_bwd(
+                _p(g), _p(A), _p(K), _p(be), _p(corr), _p(gA), _p(gK), _p(gB), _p(gS), B, NC, C, H, D, N,
+                0 if EXACT_CORRECTION_TRUE_GRADIENT else 1, _dtype_code(K), _stream()), "exact_correction_bwd")
+        return gA, gK.to(K.dtype), gB.to(be.dtype), gS, None
 
 
 # ------------------------------------------------------------------------------------------

@@ -73,6 +73,43 @@ CDSSM_API int cdssm_b200_dynamics_bwd(const void* grad_A_bar, const void* grad_v
 CDSSM_API int cdssm_b200_normalize_kq_bwd(const void* grad_K_out, const void* grad_Q_out, const void* K, const void* Q,
                                 void* grad_K, void* grad_Q, int64_t rows, int D, int dtype, void* stream);
 
+/* Backward of the intra-chunk scan.  Upstream gradients of local_h (BNC,C,H,N,D) and cum_A (BNC,C,H,N); the forward's
+ * inputs and its saved outputs (the state before step t is local_h[t-1], as in the reference) -> grad_A, grad_V in the
+ * storage type, grad_K (BNC,C,H,D) and grad_beta (BNC,C,H) in float32 (summed over the pairs of a head; zeroed and
+ * accumulated by the call).
+ * Replaces intra_chunk_scan_bwd_cuda, cdssm/csrc/kernels/intra_chunk_scan.cu:215-553 (cdssm/ops.py:123-135). */
+CDSSM_API int cdssm_b200_intra_chunk_scan_bwd(const void* grad_local_h, const void* grad_cum_A, const void* A,
+                                    const void* K, const void* V, const void* beta, const void* local_h,
+                                    const void* cum_A, void* grad_A, float* grad_K, void* grad_V, float* grad_beta,
+                                    int BNC, int C, int H, int D, int N, int dtype, void* stream);
+
+/* Backward of the correction pass: upstream gradient of corrections (B,NC,C,H,N,D), the forward's inputs and saved
+ * output -> grad_A (B,NC,C,H,N), grad_K (B,NC,C,H,D) float32, grad_beta (B,NC,C,H) float32, grad_chunk_states
+ * (B,NC,H,N,D).  reference_order = 1 reproduces the reference's backward kernel, which adds the upstream gradient of
+ * corrections[t] before walking step t back (exact_correction.cu:219-223) although its forward stores corrections[t]
+ * before step t (exact_correction.cu:90-94), and whose grad_beta is D times too large (a reduced value is reduced
+ * over the D threads again, :347-359): not the derivative of the forward, but what the reference trains with.
+ * reference_order = 0 is the true derivative.
+ * Replaces exact_correction_bwd_cuda, cdssm/csrc/kernels/exact_correction.cu:169-383 (cdssm/ops.py:188-195). */
+CDSSM_API int cdssm_b200_exact_correction_bwd(const void* grad_corrections, const void* A, const void* K,
+                                    const void* beta, const void* corrections, void* grad_A, float* grad_K,
+                                    float* grad_beta, void* grad_chunk_states, int B, int NC, int C, int H, int D,
+                                    int N, int reference_order, int dtype, void* stream);
+
+/* Backward of the inter-chunk carry: upstream gradient of chunk_states, total_A and the saved chunk_states ->
+ * grad_total_A (B,NC,H,N), grad_final_local_h (B,NC,H,N,D).
+ * Replaces inter_chunk_scan_bwd_cuda, cdssm/csrc/kernels/inter_chunk_scan.cu:89-196 (cdssm/ops.py:157-163). */
+CDSSM_API int cdssm_b200_inter_chunk_scan_bwd(const void* grad_chunk_states, const void* total_A,
+                                    const void* chunk_states, void* grad_total_A, void* grad_final_local_h,
+                                    int B, int NC, int H, int D, int N, int dtype, void* stream);
+
+/* Backward of conv1d + SiLU: grad_x (B,L,Dm) in the storage type, grad_weight (Dm,4) and grad_bias (Dm) float32
+ * (zeroed and accumulated by the call).
+ * Replaces conv1d_silu_bwd_cuda, cdssm/csrc/kernels/conv1d_silu.cu:94-219 (cdssm/ops.py:22-28). */
+CDSSM_API int cdssm_b200_conv1d_silu_bwd(const void* grad_out, const void* x, const void* weight, const void* bias,
+                               void* grad_x, float* grad_weight, float* grad_bias, int B, int L, int Dm, int dtype,
+                               void* stream);
+
 /* Intra-chunk delta-rule scan from a zero state.  A (BNC,C,H,N), K (BNC,C,H,D), V (BNC,C,H,N),
  * beta (BNC,C,H) -> local_h (BNC,C,H,N,D), cum_A (BNC,C,H,N).
  * Replaces intra_chunk_scan_fwd_cuda, cdssm/csrc/kernels/intra_chunk_scan.cu:560-609

@@ -149,3 +149,176 @@ def normalize_backward(g_out, x):
     inv = 1.0 / np.sqrt((x ** 2).sum(-1, keepdims=True) + EPS)
     xh = x * inv
     return (g_out - xh * (g_out * xh).sum(-1, keepdims=True)) * inv
+
+
+# ---------------------------------------------------------------------------------------------
+# The scan-side operators and the conv.  State rows come in complex pairs (rows 2j, 2j+1 = re, im); the stored
+# A_bar pair multiplies the state pair as a complex number (intra_chunk_scan.cu:140-152).
+def _cplx(x, axis):
+    """Pairs (2j, 2j+1) along `axis` -> complex, that axis halved."""
+    x = np.moveaxis(np.asarray(x, np.float64), axis, -1)
+    return np.moveaxis(x[..., 0::2] + 1j * x[..., 1::2], -1, axis)
+
+
+def _pairs(z, axis):
+    z = np.moveaxis(z, axis, -1)
+    out = np.empty(z.shape[:-1] + (2 * z.shape[-1],))
+    out[..., 0::2], out[..., 1::2] = z.real, z.imag
+    return np.moveaxis(out, -1, axis)
+
+
+def intra_forward(A, K, V, beta):
+    """intra_chunk_scan.cu:100-195.  A (M,C,H,N), K (M,C,H,D), V (M,C,H,N), beta (M,C,H) ->
+    local_h (M,C,H,N,D), cum_A (M,C,H,N)."""
+    a, v = _cplx(A, -1), _cplx(V, -1)                        # (M,C,H,P)
+    K, beta = np.asarray(K, np.float64), np.asarray(beta, np.float64)
+    M, C, H, P = a.shape
+    D = K.shape[-1]
+    z = np.zeros((M, H, P, D), complex)
+    ca = np.ones((M, H, P), complex)
+    lh = np.empty((M, C, H, P, D), complex)
+    cA = np.empty((M, C, H, P), complex)
+    for t in range(C):
+        k, b = K[:, t][:, :, None, :], beta[:, t][:, :, None, None]
+        u = (z * k).sum(-1, keepdims=True)
+        z = a[:, t][..., None] * (z - b * u * k) + b * v[:, t][..., None] * k
+        ca = a[:, t] * ca
+        lh[:, t], cA[:, t] = z, ca
+    return _pairs(lh, 3), _pairs(cA, 3)
+
+
+def intra_backward(g_lh, g_cA, A, K, V, beta, local_h, cum_A):
+    """Reverse walk with the SAVED forward outputs as the previous state / previous decay product
+    (intra_chunk_scan.cu:268-540).  -> grad_A, grad_K, grad_V, grad_beta."""
+    a, v = _cplx(A, -1), _cplx(V, -1)
+    K, beta = np.asarray(K, np.float64), np.asarray(beta, np.float64)
+    lh, cA = _cplx(local_h, 3), _cplx(cum_A, 3)
+    glh, gcA = _cplx(g_lh, 3), _cplx(g_cA, 3)
+    M, C, H, P = a.shape
+    Gz = np.zeros_like(lh[:, 0])
+    Gc = np.zeros_like(cA[:, 0])
+    gA = np.empty_like(a)
+    gV = np.empty_like(v)
+    gK = np.zeros_like(K)
+    gB = np.zeros_like(beta)
+    for t in range(C - 1, -1, -1):
+        Gz = Gz + glh[:, t]
+        Gc = Gc + gcA[:, t]
+        zp = lh[:, t - 1] if t > 0 else np.zeros_like(Gz)
+        cp = cA[:, t - 1] if t > 0 else np.ones_like(Gc)
+        k, b = K[:, t][:, :, None, :], beta[:, t][:, :, None, None]
+        at, vt = a[:, t][..., None], v[:, t][..., None]
+        u = (zp * k).sum(-1, keepdims=True)
+        e = zp - b * u * k
+        gA[:, t] = (Gz * np.conj(e)).sum(-1) + Gc * np.conj(cp)
+        Ge = np.conj(at) * Gz
+        s = (Gz * k).sum(-1, keepdims=True)
+        gV[:, t] = (b * s)[..., 0]
+        w = (Ge * k).sum(-1, keepdims=True)
+        gB[:, t] = ((s * np.conj(vt)).real - (w * np.conj(u)).real).sum((2, 3))
+        Gu = -b * w
+        gK[:, t] = (b * (Gz * np.conj(vt)).real - b * (Ge * np.conj(u)).real + (Gu * np.conj(zp)).real).sum(2)
+        Gz = Ge + Gu * k
+        Gc = np.conj(a[:, t]) * Gc
+    return _pairs(gA, -1), gK, _pairs(gV, -1), gB
+
+
+def inter_forward(total_A, final_h):
+    """inter_chunk_scan.cu:52-84.  total_A (B,NC,H,N), final_h (B,NC,H,N,D) -> chunk_states (B,NC,H,N,D)."""
+    a, h = _cplx(total_A, -1), _cplx(final_h, 3)
+    s = np.zeros_like(h[:, 0])
+    out = np.empty_like(h)
+    for c in range(a.shape[1]):
+        out[:, c] = s
+        s = a[:, c][..., None] * s + h[:, c]
+    return _pairs(out, 3)
+
+
+def inter_backward(g_states, total_A, chunk_states):
+    """inter_chunk_scan.cu:115-190 (the saved chunk_states are the forward's s_c).  -> grad_total_A, grad_final_h."""
+    a, s, g = _cplx(total_A, -1), _cplx(chunk_states, 3), _cplx(g_states, 3)
+    G = np.zeros_like(s[:, 0])
+    gA, gH = np.empty_like(a), np.empty_like(s)
+    for c in range(a.shape[1] - 1, -1, -1):
+        gH[:, c] = G
+        gA[:, c] = (G * np.conj(s[:, c])).sum(-1)
+        G = np.conj(a[:, c])[..., None] * G + g[:, c]
+    return _pairs(gA, -1), _pairs(gH, 3)
+
+
+def correction_forward(A, K, beta, states):
+    """exact_correction.cu:83-150.  A (B,NC,C,H,N), K (B,NC,C,H,D), beta (B,NC,C,H), states (B,NC,H,N,D) ->
+    corrections (B,NC,C,H,N,D): the state BEFORE each step."""
+    a = _cplx(A, -1)
+    K, beta = np.asarray(K, np.float64), np.asarray(beta, np.float64)
+    r = _cplx(states, 3)
+    C = a.shape[2]
+    out = np.empty(a.shape[:2] + (C,) + r.shape[2:], complex)
+    for t in range(C):
+        out[:, :, t] = r
+        k, b = K[:, :, t][:, :, :, None, :], beta[:, :, t][:, :, :, None, None]
+        u = (r * k).sum(-1, keepdims=True)
+        r = a[:, :, t][..., None] * (r - b * u * k)
+    return _pairs(out, 4)
+
+
+def correction_backward(g_corr, A, K, beta, states, corrections, reference_order=False):
+    """exact_correction.cu:230-375, with the saved corrections as the state before each step.
+    -> grad_A, grad_K, grad_beta, grad_states.  reference_order=True adds the upstream gradient of corrections[t]
+    BEFORE step t is walked back, as the reference kernel does (exact_correction.cu:219-223): that is not the
+    derivative of the forward (which stores corrections[t] before the step), but it is what the reference computes."""
+    a = _cplx(A, -1)
+    K, beta = np.asarray(K, np.float64), np.asarray(beta, np.float64)
+    rs, g = _cplx(corrections, 4), _cplx(g_corr, 4)
+    C = a.shape[2]
+    Gr = np.zeros_like(rs[:, :, 0])
+    gA = np.empty_like(a)
+    gK = np.zeros_like(K)
+    gB = np.zeros_like(beta)
+    for t in range(C - 1, -1, -1):
+        r = rs[:, :, t]
+        if reference_order:
+            Gr = Gr + g[:, :, t]
+        k, b = K[:, :, t][:, :, :, None, :], beta[:, :, t][:, :, :, None, None]
+        at = a[:, :, t][..., None]
+        u = (r * k).sum(-1, keepdims=True)
+        e = r - b * u * k
+        gA[:, :, t] = (Gr * np.conj(e)).sum(-1)
+        Ge = np.conj(at) * Gr
+        w = (Ge * k).sum(-1, keepdims=True)
+        gB[:, :, t] = -(w * np.conj(u)).real.sum((3, 4))
+        if reference_order:      # the reference reduces an already reduced value over its D threads again (:347-359)
+            gB[:, :, t] *= K.shape[-1]
+        Gu = -b * w
+        gK[:, :, t] = (-b * (Ge * np.conj(u)).real + (Gu * np.conj(r)).real).sum(3)
+        Gr = Ge + Gu * k
+        if not reference_order:
+            Gr = Gr + g[:, :, t]
+    return _pairs(gA, -1), gK, gB, _pairs(Gr, 3)
+
+
+def _silu(p):
+    return p * _sig(p)
+
+
+def conv_forward(x, w, bias):
+    """conv1d_silu.cu:25-90.  x (B,L,Dm), w (Dm,4), bias (Dm): causal 4-tap depthwise conv + SiLU."""
+    x, w, bias = (np.asarray(t, np.float64) for t in (x, w, bias))
+    B, L, Dm = x.shape
+    xp = np.concatenate([np.zeros((B, 3, Dm)), x], 1)
+    pre = bias + sum(w[:, j] * xp[:, j:j + L] for j in range(4))
+    return _silu(pre)
+
+
+def conv_backward(g_out, x, w, bias):
+    """conv1d_silu.cu:94-219.  -> grad_x, grad_w (Dm,4), grad_bias."""
+    x, w, bias, g_out = (np.asarray(t, np.float64) for t in (x, w, bias, g_out))
+    B, L, Dm = x.shape
+    xp = np.concatenate([np.zeros((B, 3, Dm)), x], 1)
+    pre = bias + sum(w[:, j] * xp[:, j:j + L] for j in range(4))
+    sg = _sig(pre)
+    gp = g_out * sg * (1 + pre * (1 - sg))
+    gpp = np.concatenate([gp, np.zeros((B, 3, Dm))], 1)
+    gx = sum(w[:, j] * gpp[:, 3 - j:3 - j + L] for j in range(4))
+    gw = np.stack([(gp * xp[:, j:j + L]).sum((0, 1)) for j in range(4)], -1)
+    return gx, gw, gp.sum((0, 1))

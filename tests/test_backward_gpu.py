@@ -48,9 +48,91 @@ def test_normalize_backward(ops, orc, dtype, tol, rows, D):
         assert np.abs(to_np(got) - want).max() <= tol * np.abs(want).max()
 
 
-def test_scan_side_backward_is_not_implemented(ops):
-    x = torch.randn(1, 8, 16, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    w = torch.randn(16, 1, 4, device="cuda", dtype=torch.bfloat16)
-    out = ops.CUDAConv1dSiLUOp.apply(x, w, torch.zeros(16, device="cuda", dtype=torch.bfloat16))
-    with pytest.raises(NotImplementedError):
-        out.sum().backward()
+def _r(orc, rng, shape, dtype, scale=1.0, lo=None, hi=None):
+    a = (rng.uniform(lo, hi, shape) if lo is not None else rng.standard_normal(shape) * scale).astype(np.float32)
+    return orc.bf16_round(a) if dtype == torch.bfloat16 else a
+
+
+def _t(a, dtype, grad=True):
+    t = torch.from_numpy(a).cuda().to(dtype)
+    return t.requires_grad_(True) if grad else t
+
+
+def _check(got, want, tol, what):
+    want = np.asarray(want)
+    err = np.abs(to_np(got) - want).max() / max(np.abs(want).max(), 1e-30)
+    assert err <= tol, (what, err)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("M,C,H,N,D", [(3, 16, 2, 2, 64), (2, 9, 3, 4, 40), (1, 64, 4, 2, 128)])
+def test_intra_chunk_scan_backward(ops, orc, dtype, tol, M, C, H, N, D):
+    """The kernel and the oracle both take the SAVED forward outputs as the previous states, so both see the same
+    (for bf16: rounded) values; the oracle's forward supplies them."""
+    from oracle import grad_oracle as go
+    rng = np.random.default_rng(C + D)
+    A = _r(orc, rng, (M, C, H, N), dtype, lo=-0.7, hi=0.7)
+    K = _r(orc, rng, (M, C, H, D), dtype, scale=1.0 / np.sqrt(D))
+    V = _r(orc, rng, (M, C, H, N), dtype)
+    be = _r(orc, rng, (M, C, H), dtype, lo=0.1, hi=0.9)
+    u1 = _r(orc, rng, (M, C, H, N, D), dtype)
+    u2 = _r(orc, rng, (M, C, H, N), dtype)
+    tA, tK, tV, tb = (_t(x, dtype) for x in (A, K, V, be))
+    lh, cA = ops.IntraChunkScanFn.apply(tA, tK, tV, tb, N)
+    torch.autograd.backward([lh, cA], [_t(u1, dtype, False), _t(u2, dtype, False)])
+    want = go.intra_backward(u1, u2, A, K, V, be, to_np(lh), to_np(cA))
+    for got, w, name in zip((tA.grad, tK.grad, tV.grad, tb.grad), want, ("A", "K", "V", "beta")):
+        assert got.dtype == dtype
+        _check(got, w, tol, name)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("B,NC,C,H,N,D", [(2, 3, 16, 2, 2, 64), (1, 4, 8, 3, 4, 40), (1, 2, 32, 4, 2, 128)])
+def test_inter_chunk_and_correction_backward(ops, orc, dtype, tol, B, NC, C, H, N, D):
+    from oracle import grad_oracle as go
+    rng = np.random.default_rng(NC + D)
+    tot = _r(orc, rng, (B, NC, H, N), dtype, lo=-0.7, hi=0.7)
+    fin = _r(orc, rng, (B, NC, H, N, D), dtype)
+    up = _r(orc, rng, (B, NC, H, N, D), dtype)
+    ta, tf = _t(tot, dtype), _t(fin, dtype)
+    cs = ops.InterChunkScanFn.apply(ta, tf, N)
+    cs.backward(_t(up, dtype, False))
+    wA, wH = go.inter_backward(up, tot, to_np(cs))
+    _check(ta.grad, wA, tol, "total_A")
+    _check(tf.grad, wH, tol, "final_local_h")
+    A = _r(orc, rng, (B, NC, C, H, N), dtype, lo=-0.7, hi=0.7)
+    K = _r(orc, rng, (B, NC, C, H, D), dtype, scale=1.0 / np.sqrt(D))
+    be = _r(orc, rng, (B, NC, C, H), dtype, lo=0.1, hi=0.9)
+    st = _r(orc, rng, (B, NC, H, N, D), dtype)
+    upc = _r(orc, rng, (B, NC, C, H, N, D), dtype)
+    tA, tK, tb, ts = (_t(x, dtype) for x in (A, K, be, st))
+    for true_gradient in (True, False):        # the derivative of the forward / the reference kernel's order
+        for t in (tA, tK, tb, ts):
+            t.grad = None
+        ops.EXACT_CORRECTION_TRUE_GRADIENT = true_gradient
+        try:
+            corr = ops.ExactCorrectionFn.apply(tA, tK, tb, ts, N)
+            corr.backward(_t(upc, dtype, False))
+        finally:
+            ops.EXACT_CORRECTION_TRUE_GRADIENT = False
+        want = go.correction_backward(upc, A, K, be, st, to_np(corr), reference_order=not true_gradient)
+        for got, w, name in zip((tA.grad, tK.grad, tb.grad, ts.grad), want, ("A", "K", "beta", "chunk_states")):
+            _check(got, w, tol, (name, true_gradient))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("B,L,Dm", [(2, 150, 256), (1, 5, 48), (3, 64, 130)])
+def test_conv_backward(ops, orc, dtype, tol, B, L, Dm):
+    from oracle import grad_oracle as go
+    rng = np.random.default_rng(L + Dm)
+    x = _r(orc, rng, (B, L, Dm), dtype)
+    w = _r(orc, rng, (Dm, 1, 4), dtype, scale=0.5)
+    b = _r(orc, rng, (Dm,), dtype, scale=0.2)
+    up = _r(orc, rng, (B, L, Dm), dtype)
+    tx, tw, tb = (_t(a, dtype) for a in (x, w, b))
+    ops.CUDAConv1dSiLUOp.apply(tx, tw, tb).backward(_t(up, dtype, False))
+    gx, gw, gb = go.conv_backward(up, x, w.reshape(Dm, 4), b)
+    assert tw.grad.shape == (Dm, 1, 4)
+    _check(tx.grad, gx, tol, "x")
+    _check(tw.grad.reshape(Dm, 4), gw, tol, "weight")
+    _check(tb.grad, gb, tol, "bias")

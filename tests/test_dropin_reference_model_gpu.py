@@ -114,6 +114,23 @@ def test_reference_block_runs_on_our_operators(ops, N):
         assert rel_err(to_np(y_ours), to_np(y_ref)) <= BF16_TOL, "reference block on our operators differs"
         assert rel_err(to_np(y_ours0), to_np(y_ref0)) <= BF16_TOL
         assert rel_err(to_np(y_model), to_np(y_ref)) <= BF16_TOL
+        # (c) a training step: backward through the reference block on our six operators against the same block on
+        # the reference's own backward kernels
+        probe = torch.randn_like(y_ref)
+        grads = []
+        for b_ in (blk, blk_ref):
+            b_.zero_grad(set_to_none=True)
+            xin = x.clone().requires_grad_(True)
+            out, _ = b_(xin, v_first)
+            (out.float() * probe.float()).sum().backward()
+            grads.append({"x": xin.grad, **{k: p.grad for k, p in b_.named_parameters() if p.grad is not None}})
+        assert set(grads[0]) == set(grads[1]) and "gate_proj.weight" in grads[0] and "log_dt_scale" in grads[0]
+        for name in grads[0]:
+            ref_g = grads[1][name].float()
+            if float(ref_g.abs().max()) == 0.0:
+                assert float(grads[0][name].float().abs().max()) == 0.0, name
+                continue
+            assert rel_err(to_np(grads[0][name]), to_np(ref_g)) <= 5e-2, name
     finally:
         _purge()
 

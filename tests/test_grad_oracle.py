@@ -68,3 +68,75 @@ def test_normalize_backward_is_the_derivative_of_the_forward():
         m[i] -= h
         fd[i] = ((go.normalize_forward(p) - go.normalize_forward(m)) * up).sum() / (2 * h)
     assert np.abs(g - fd).max() <= 1e-6 * max(np.abs(fd).max(), 1.0)
+
+
+def _fd(loss, x, h=1e-6):
+    fd = np.zeros_like(x)
+    for i in np.ndindex(*x.shape):
+        p, m = x.copy(), x.copy()
+        p[i] += h
+        m[i] -= h
+        fd[i] = (loss(p) - loss(m)) / (2 * h)
+    return fd
+
+
+def _close(a, b, tol=2e-6):
+    assert np.abs(a - b).max() <= tol * max(np.abs(b).max(), 1.0)
+
+
+def test_intra_forward_matches_the_c_oracle_and_backward_is_its_derivative(orc):
+    rng = np.random.default_rng(1)
+    M, C, H, N, D = 2, 5, 2, 4, 3
+    A = rng.uniform(-0.9, 0.9, (M, C, H, N))
+    K = rng.standard_normal((M, C, H, D)) * 0.6
+    V = rng.standard_normal((M, C, H, N))
+    beta = rng.uniform(0.1, 0.9, (M, C, H))
+    lh, cA = go.intra_forward(A, K, V, beta)
+    wlh, wcA = orc.intra_chunk(A.astype(np.float32), K.astype(np.float32), V.astype(np.float32), beta.astype(np.float32), N)
+    _close(lh, wlh, 1e-5)
+    _close(cA, wcA, 1e-5)
+    u1, u2 = rng.standard_normal(lh.shape), rng.standard_normal(cA.shape)
+    loss = lambda A_, K_, V_, b_: float((go.intra_forward(A_, K_, V_, b_)[0] * u1).sum() + (go.intra_forward(A_, K_, V_, b_)[1] * u2).sum())
+    gA, gK, gV, gB = go.intra_backward(u1, u2, A, K, V, beta, lh, cA)
+    _close(gA, _fd(lambda t: loss(t, K, V, beta), A))
+    _close(gK, _fd(lambda t: loss(A, t, V, beta), K))
+    _close(gV, _fd(lambda t: loss(A, K, t, beta), V))
+    _close(gB, _fd(lambda t: loss(A, K, V, t), beta))
+
+
+def test_inter_and_correction_backward_are_the_derivatives(orc):
+    rng = np.random.default_rng(2)
+    B, NC, C, H, N, D = 1, 4, 3, 2, 2, 3
+    tA = rng.uniform(-0.9, 0.9, (B, NC, H, N))
+    fh = rng.standard_normal((B, NC, H, N, D))
+    cs = go.inter_forward(tA, fh)
+    _close(cs, orc.inter_chunk(tA.astype(np.float32), fh.astype(np.float32), N), 1e-5)
+    up = rng.standard_normal(cs.shape)
+    gA, gH = go.inter_backward(up, tA, cs)
+    _close(gA, _fd(lambda t: float((go.inter_forward(t, fh) * up).sum()), tA))
+    _close(gH, _fd(lambda t: float((go.inter_forward(tA, t) * up).sum()), fh))
+    A = rng.uniform(-0.9, 0.9, (B, NC, C, H, N))
+    K = rng.standard_normal((B, NC, C, H, D)) * 0.6
+    beta = rng.uniform(0.1, 0.9, (B, NC, C, H))
+    corr = go.correction_forward(A, K, beta, cs)
+    _close(corr, orc.exact_correction(A.astype(np.float32), K.astype(np.float32), beta.astype(np.float32),
+                                      cs.astype(np.float32), N), 1e-5)
+    up = rng.standard_normal(corr.shape)
+    gA, gK, gB, gS = go.correction_backward(up, A, K, beta, cs, corr)
+    _close(gA, _fd(lambda t: float((go.correction_forward(t, K, beta, cs) * up).sum()), A))
+    _close(gK, _fd(lambda t: float((go.correction_forward(A, t, beta, cs) * up).sum()), K))
+    _close(gB, _fd(lambda t: float((go.correction_forward(A, K, t, cs) * up).sum()), beta))
+    _close(gS, _fd(lambda t: float((go.correction_forward(A, K, beta, t) * up).sum()), cs))
+
+
+def test_conv_backward_is_the_derivative(orc):
+    rng = np.random.default_rng(3)
+    B, L, Dm = 2, 7, 3
+    x, w, b = rng.standard_normal((B, L, Dm)), rng.standard_normal((Dm, 4)), rng.standard_normal(Dm)
+    out = go.conv_forward(x, w, b)
+    _close(out, orc.conv1d_silu(x.astype(np.float32), w.astype(np.float32), b.astype(np.float32)), 1e-5)
+    up = rng.standard_normal(out.shape)
+    gx, gw, gb = go.conv_backward(up, x, w, b)
+    _close(gx, _fd(lambda t: float((go.conv_forward(t, w, b) * up).sum()), x))
+    _close(gw, _fd(lambda t: float((go.conv_forward(x, t, b) * up).sum()), w))
+    _close(gb, _fd(lambda t: float((go.conv_forward(x, w, t) * up).sum()), b))

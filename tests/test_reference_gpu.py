@@ -95,3 +95,46 @@ def test_backward_kernels_against_reference_backward_kernels(ops, orc, ref):
     torch.autograd.backward(ops.NormalizeKQFn.apply(kt, qt), [gK, gQ])
     assert rel_err(to_np(kt.grad), to_np(wK)) <= BF16_TOL / 2
     assert rel_err(to_np(qt.grad), to_np(wQ)) <= BF16_TOL / 2
+
+
+def test_scan_side_backward_kernels_against_reference_backward_kernels(ops, orc, ref):
+    """intra / inter / correction / conv backward against the reference's own backward kernels, each fed with the
+    reference's own forward outputs as the saved tensors."""
+    B, NC, C, H, N, D = 2, 3, 64, 4, 2, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    A = (rn(B * NC, C, H, N) * 0.4).bfloat16()
+    K = (rn(B * NC, C, H, D) / 8).bfloat16()
+    V, be = rn(B * NC, C, H, N).bfloat16(), torch.rand(B * NC, C, H, generator=g, device="cuda").bfloat16()
+    lh, cA = ref.intra_chunk_scan_fwd_cuda(A, K, V, be, N)
+    u1, u2 = rn(*lh.shape).bfloat16(), rn(*cA.shape).bfloat16()
+    want = ref.intra_chunk_scan_bwd_cuda(u1, u2, A, K, V, be, lh, cA, N)
+    ts = [t.clone().requires_grad_(True) for t in (A, K, V, be)]
+    torch.autograd.backward(ops.IntraChunkScanFn.apply(*ts, N), [u1, u2])
+    for t, w, name in zip(ts, want, ("A", "K", "V", "beta")):
+        assert rel_err(to_np(t.grad), to_np(w)) <= BF16_TOL, name
+    # inter-chunk
+    tot, fin = (rn(B, NC, H, N) * 0.4).bfloat16(), rn(B, NC, H, N, D).bfloat16()
+    cs = ref.inter_chunk_scan_fwd_cuda(tot, fin, N)
+    up = rn(*cs.shape).bfloat16()
+    wA, wH = ref.inter_chunk_scan_bwd_cuda(up, tot, cs, N)
+    ta, tf = tot.clone().requires_grad_(True), fin.clone().requires_grad_(True)
+    ops.InterChunkScanFn.apply(ta, tf, N).backward(up)
+    assert rel_err(to_np(ta.grad), to_np(wA)) <= BF16_TOL and rel_err(to_np(tf.grad), to_np(wH)) <= BF16_TOL
+    # correction
+    A5, K5, b5 = A.view(B, NC, C, H, N), K.view(B, NC, C, H, D), be.view(B, NC, C, H)
+    corr = ref.exact_correction_fwd_cuda(A5, K5, b5, cs, N)
+    upc = rn(*corr.shape).bfloat16()
+    want = ref.exact_correction_bwd_cuda(upc, A5, K5, b5, cs, corr, N)
+    ts = [t.clone().requires_grad_(True) for t in (A5, K5, b5, cs)]
+    ops.ExactCorrectionFn.apply(*ts, N).backward(upc)
+    for t, w, name in zip(ts, want, ("A", "K", "beta", "chunk_states")):
+        assert rel_err(to_np(t.grad), to_np(w)) <= BF16_TOL, name
+    # conv
+    x, w4 = rn(2, 100, 256).bfloat16(), (rn(256, 1, 4) / 2).bfloat16()
+    bias, upx = (rn(256) / 5).bfloat16(), rn(2, 100, 256).bfloat16()
+    want = ref.conv1d_silu_bwd_cuda(x, w4, bias, upx)
+    ts = [t.clone().requires_grad_(True) for t in (x, w4, bias)]
+    ops.CUDAConv1dSiLUOp.apply(*ts).backward(upx)
+    for t, w, name in zip(ts, want, ("x", "weight", "bias")):
+        assert rel_err(to_np(t.grad), to_np(w).reshape(t.shape)) <= BF16_TOL, name
