@@ -92,5 +92,3 @@ def test_errors_mirror_reference_checks(ops):
     A = torch.zeros(1, 4, 1, 2, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):                       # intra_chunk_scan.cu:584
         ops.IntraChunkScanFn.apply(A, K, A, A[..., 0], 2)
-    with pytest.raises(NotImplementedError):
-        ops.NormalizeKQFn.backward(None, None, None)
