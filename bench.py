@@ -457,7 +457,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--segments", type=int, default=0, help="cfg4: segments per sequence over all GPUs (default: the workload's)")
-    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (1 = the CUDA-core kernels instead of the tensor-core passes)")
+    ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (1 = the CUDA-core kernels instead of the tensor-core passes, 4096 = float32 transition)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -602,6 +602,15 @@ def main():
             summary_step()
             extra["summary_ms"] = timed(summary_step, args.steps) / args.steps
         t_end = time.time()
+        # untimed: how much of the output is finite.  At 2^20 tokens the reference's own arithmetic (bfloat16 A_bar,
+        # carry without erasure) overflows on some heads; ops.FP32_DECAY (--flags 4096) is the bounded variant.
+        out_now = step()[0]
+        torch.cuda.synchronize()
+        fin_cnt = torch.stack([torch.isfinite(out_now.float()).sum(), torch.tensor(out_now.numel(), device=dev)]).double()
+        if dist is not None:
+            dist.all_reduce(fin_cnt)
+        finite_fraction = float(fin_cnt[0] / fin_cnt[1])
+        del out_now
         parity_err = None
         if rank == 0 and not seq_par:
             step()
@@ -657,6 +666,7 @@ def main():
                                                "kernels at cfg2 L=4096, scaled by tokens")
         if "segment_passes_ms" in extra:
             line["segment_passes_ms"] = extra["segment_passes_ms"]
+        line["output_finite_fraction"] = finite_fraction
         if not args.no_cpu_baseline and world == 1 and not seq_par:
             try:
                 rg = reference_gpu_leg(w, q, k, v, gate, lds, rope, consts, ops)

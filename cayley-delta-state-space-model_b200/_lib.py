@@ -44,7 +44,7 @@ SIGNATURES = {
     "cdssm_b200_conv1d_silu_step": (_I, [_P, _c_int64, _P, _P, _P, _P, _I, _I, _I, _P]),
     "cdssm_b200_scan_fused_workspace_bytes": (_c_size_t, [_I] * 6),
     "cdssm_b200_scan_fused_fwd": (_I, [_P] * 11 + [_c_size_t] + [_F] * 6 + [_I] * 9 + [_P]),
-    "cdssm_b200_scan_summary_fwd": (_I, [_P] * 9 + [_c_size_t] + [_F] * 5 + [_I] * 9 + [_P]),
+    "cdssm_b200_scan_summary_fwd": (_I, [_P] * 9 + [_c_size_t] + [_F] * 5 + [_I] * 10 + [_P]),
     "cdssm_b200_scan_fused_segmented_fwd": (_I, [_P] * 10 + [_c_size_t] + [_F] * 6 + [_I] * 10 + [_P]),
     "cdssm_b200_compose_carries": (_I, [_P] * 6 + [_I] * 5 + [_c_int64, _c_int64, _P]),
     "cdssm_b200_scan_fused_fwd_noalloc": (_I, [_P] * 10 + [_F] * 6 + [_I] * 9 + [_P]),

@@ -42,5 +42,5 @@ extern "C" int cdssm_b200_selftest_bounded_wait(int* status_dev, uint64_t limit_
     return cdssm::check_launch();
 }
 
-extern "C" int cdssm_b200_version(void) { return 200; }
+extern "C" int cdssm_b200_version(void) { return 201; }
 extern "C" int cdssm_b200_last_cuda_error(void) { return cdssm::last_cuda_error_ref(); }

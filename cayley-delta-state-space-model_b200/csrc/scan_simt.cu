@@ -114,6 +114,7 @@ struct ScanArgs {
     int run_local;        // 0: the workspace already holds this input's local pass
     int run_output;       // 0: stop after the carry pass (another kernel writes y)
     int publish;          // 0: summary only, the carry pass leaves the local results in place
+    int fp32_decay;       // 1: the transition a_t keeps float32 precision (the reference stores it as bf16)
     float* ws_gamma;   // (B,NC,H,NP,2)
     float* ws_state;   // (B,NC,H,NP,2,D): z_{C-1} after the local pass, s_c after the carry pass
     DynConsts dc;
@@ -157,8 +158,10 @@ __device__ __forceinline__ void stage_dynamics(const ScanArgs& a, ChunkScalars& 
             float vp;
             dyn_pair<IO<T>::kBf16>(IO<T>::ld(gr + j * H + hd), IO<T>::ld(gr + (NH + j) * H + hd), freq, pos, ds,
                      ar, ai, vp);
-            ar = IO<T>::rnd(ar);
-            ai = IO<T>::rnd(ai);
+            if (!a.fp32_decay) {
+                ar = IO<T>::rnd(ar);
+                ai = IO<T>::rnd(ai);
+            }
             vp = IO<T>::rnd(vp);
             be = IO<T>::rnd(ds.beta);
             sc = IO<T>::rnd(ds.sel_c);
@@ -895,7 +898,8 @@ unsigned long long wait_limit_ns();   // c_abi.cu
 bool scan_wa_supported(int D, int N, int C, int H, int dtype);
 size_t scan_wa_record_bytes(int B, int L, int H, int C);
 int scan_wa_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
-                     void* rec, const DynConsts& dc, int B, int L, int H, int C, int pos0, int segs, cudaStream_t st);
+                     void* rec, const DynConsts& dc, int B, int L, int H, int C, int pos0, int segs, int fp32_decay,
+                     cudaStream_t st);
 int scan_wa_pass(bool output, const void* q, const void* k, const void* rec, float* ws_gamma, float* ws_state, void* y,
                  int* status, float shortcut_scale, int B, int L, int H, int D, unsigned long long wait_ns, int withhold,
                  cudaStream_t st);
@@ -953,6 +957,7 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     a.run_local = (flags & CDSSM_SCAN_REUSE_LOCAL) ? 0 : 1;
     a.run_output = 1;
     a.publish = summary_only ? 0 : 1;
+    a.fp32_decay = (flags & CDSSM_SCAN_FP32_DECAY) ? 1 : 0;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
     a.shortcut_scale = shortcut_scale;
     a.B = B; a.L = L; a.H = H; a.D = D; a.N = N; a.C = C; a.pos0 = pos0;
@@ -975,10 +980,6 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
                                             cudaMemcpyDeviceToDevice, st));
         return rc;
     }
-    // Four-chain tensor-core kernels for the local and the output pass, with the CUDA-core carry pass between
-    // them: measured faster than the CUDA-core walks at every size tried on B200 (2.7x at 64 chunk-head-groups,
-    // 1.2x at 4096), so they are taken whenever the shapes allow and nothing else was asked for.  (Bits 256 /
-    // 512 keep the CUDA-core local / output pass: used by the tests to check each tensor-core pass alone.)
     // Warp-autonomous tensor-core passes (scan_wa.cu) for the local and the output pass, with the CUDA-core
     // carry pass between them: the default wherever the shapes allow.  (Bits 256 / 512 keep the CUDA-core
     // local / output pass: used by the tests to check each tensor-core pass alone.)
@@ -994,7 +995,8 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
         const int withhold = (flags & CDSSM_SCAN_TEST_WITHHOLD) ? 1 : 0;
         const unsigned long long limit = wait_limit_ns();
         void* rec = reinterpret_cast<char*>(a.ws_state) + align256((size_t)a.units * 2 * D * sizeof(float));
-        if (int rc = scan_wa_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, C, pos0, segs, st))
+        if (int rc = scan_wa_dynamics(v, gate_raw, log_dt_scale, rope_freqs, rec, a.dc, B, L, H, C, pos0, segs,
+                                      a.fp32_decay, st))
             return rc;
         if (a.run_local && tc_local) {
             if (int rc = scan_wa_pass(false, q, k, rec, a.ws_gamma, a.ws_state, nullptr, status, shortcut_scale, B, L, H,
@@ -1077,12 +1079,13 @@ extern "C" int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const v
                                            void* workspace, size_t workspace_bytes, float gating_c,
                                            float omega_thresh, float adt_delta, float adt_smoothness,
                                            float adt_eps, int B, int L, int H, int D, int N, int C, int pos0,
-                                           int segs, int dtype, void* stream) {
+                                           int segs, int dtype, int flags, void* stream) {
     if (!carry_out || !total_decay) return CDSSM_ERR_BAD_ARG;
+    if (flags & ~CDSSM_SCAN_FP32_DECAY) return CDSSM_ERR_BAD_ARG;   // the only option that applies to a summary
     return scan_fused_impl(nullptr, k, v, gate_raw, log_dt_scale, rope_freqs, h0, nullptr, carry_out,
                            nullptr, total_decay, true, workspace, workspace_bytes, gating_c, omega_thresh,
                            adt_delta, adt_smoothness, adt_eps, 0.f, B, L, H, D, N, C, pos0, segs, dtype,
-                           CDSSM_SCAN_DEFAULT, stream);
+                           flags, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

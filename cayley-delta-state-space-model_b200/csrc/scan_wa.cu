@@ -111,8 +111,9 @@ __device__ __forceinline__ ItemPos item_pos(const Args& a, int item) {
     return p;
 }
 
-// Record of one (token, head): {a_re, a_im | vg_re, vg_im | beta, sel_C | -} as bf16 pairs (all of them are
-// bf16 values in the reference's storage).  Layout (B, blocks of 32 tokens, H, 32): the 32 tokens of a head's
+// Record of one (token, head): {a_re | a_im | vg_re, vg_im | beta, sel_C}: the transition as two floats (bf16
+// values like the reference's storage unless the caller asked for a float32 transition), the rest as bf16
+// pairs.  Layout (B, blocks of 32 tokens, H, 32): the 32 tokens of a head's
 // sub-block are contiguous, so a warp fetches its step with one 512-byte load.
 __device__ __forceinline__ size_t rec_index(const Args& a, int steps, int b, int c, int sub, int hd, int tl) {
     return ((((size_t)b * a.NC + c) * steps + sub) * a.H + hd) * kSub + tl;
@@ -273,10 +274,10 @@ struct Tok {   // per-token quantities of one sub-block step, prepared one step 
 // more than 1e-30 (then, or with the zero padding behind the sequence end, the explicit walk is taken).
 __device__ __forceinline__ Tok prepare(const uint4& rec, int tl) {
     Tok k;
-    k.at = {bf_lo(rec.x), bf_hi(rec.x)};
-    k.vg = {bf_lo(rec.y), bf_hi(rec.y)};
-    k.be = bf_lo(rec.z);
-    k.sc = bf_hi(rec.z);
+    k.at = {__uint_as_float(rec.x), __uint_as_float(rec.y)};
+    k.vg = {bf_lo(rec.z), bf_hi(rec.z)};
+    k.be = bf_lo(rec.w);
+    k.sc = bf_hi(rec.w);
     const bool lo = tl < 16;
     // lanes < 16: exclusive suffix product inside the first half; lanes >= 16: inclusive prefix inside the second
     cplx X = k.at;
@@ -817,6 +818,7 @@ struct DynArgs {
     uint4* rec;
     DynConsts dc;
     int B, L, H, NB, pos0, segs;   // NB: 32-token blocks per batch row (chunks padded to full length)
+    int fp32_decay;                // 0: the transition is rounded to bf16 like the reference's A_bar store
 };
 __global__ void __launch_bounds__(256) wa_dynamics_kernel(const DynArgs a) {
     using T = __nv_bfloat16;
@@ -837,12 +839,16 @@ __global__ void __launch_bounds__(256) wa_dynamics_kernel(const DynArgs a) {
     float ar, ai, vp;
     dyn_pair<true>(g0, g1, freq, pos, ds, ar, ai, vp);
     vp = bfr(vp);
+    if (!a.fp32_decay) {
+        ar = bfr(ar);
+        ai = bfr(ai);
+    }
     const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v + ((size_t)bl * H + hd) * 2);
     uint4 r;
-    r.x = pack2(ar, ai);
-    r.y = pack2(__low2float(v2) * vp, __high2float(v2) * vp);
-    r.z = pack2(ds.beta, ds.sel_c);
-    r.w = 0u;
+    r.x = __float_as_uint(ar);
+    r.y = __float_as_uint(ai);
+    r.z = pack2(__low2float(v2) * vp, __high2float(v2) * vp);
+    r.w = pack2(ds.beta, ds.sel_c);
     a.rec[(((size_t)b * a.NB + (l >> 5)) * H + hd) * kSub + (l & 31)] = r;
 }
 
@@ -917,7 +923,8 @@ size_t scan_wa_record_bytes(int B, int L, int H, int C) {
 
 // Dynamics pre-pass: fills rec (scan_wa_record_bytes bytes) for both scan passes.
 int scan_wa_dynamics(const void* v, const void* gate_raw, const float* log_dt_scale, const float* rope_freqs,
-                     void* rec, const DynConsts& dc, int B, int L, int H, int C, int pos0, int segs, cudaStream_t st) {
+                     void* rec, const DynConsts& dc, int B, int L, int H, int C, int pos0, int segs, int fp32_decay,
+                     cudaStream_t st) {
     wa::DynArgs d;
     d.v = static_cast<const __nv_bfloat16*>(v);
     d.gate_raw = static_cast<const __nv_bfloat16*>(gate_raw);
@@ -925,6 +932,7 @@ int scan_wa_dynamics(const void* v, const void* gate_raw, const float* log_dt_sc
     d.rec = static_cast<uint4*>(rec);
     d.dc = dc;
     d.B = B; d.L = L; d.H = H; d.NB = ((L + C - 1) / C) * (C / wa::kSub); d.pos0 = pos0; d.segs = segs;
+    d.fp32_decay = fp32_decay;
     const long long total = (long long)B * L * H;
     wa::wa_dynamics_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d);
     return check_launch();

@@ -298,6 +298,8 @@ REUSE_LOCAL = 8
 EXACT = 32
 TENSOR_CORE_WA = 128
 TEST_WITHHOLD = 2048   # self-test of the bounded waits: see include/cdssm_b200.h
+FP32_DECAY = 4096      # keep the transition A_bar in float32 (NOT the reference's arithmetic): the reference's
+#                        bfloat16 A_bar lets its carry grow without bound over some 1e5 tokens, see the header
 
 _workspaces = {}
 
@@ -578,10 +580,10 @@ def selftest_bounded_wait(limit_ns: int = 1_000_000, device=None) -> int:
 def scan_summary(k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor, rope_freqs: Tensor,
                  gating_c: float, omega_thresh: float, adt_delta: float, adt_smoothness: float,
                  adt_eps: float, n_heads: int, state_dim: int, chunk_size: int, h0: Tensor = None, *,
-                 pos0: int = 0, segs: int = 1):
+                 pos0: int = 0, segs: int = 1, flags: int = 0):
     """Summary of chunk-aligned segments: (carry_out (B,H,N,D), total_decay (B,H,N)) float32, the
     carry after the last chunk for carry-in h0 and the product of the chunk decays.  Reads k, v and
-    the gates only (about half of the scan's bytes)."""
+    the gates only (about half of the scan's bytes).  Of ``flags`` only FP32_DECAY applies."""
     k = _prep(k, name="k")
     v = _prep(v, dtype=k.dtype, name="v")
     g = _prep(gate_raw, dtype=k.dtype, name="gate_raw")
@@ -600,7 +602,7 @@ def scan_summary(k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: Tensor, r
         check(_lib.lib().cdssm_b200_scan_summary_fwd(
             _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(h0), _p(carry), _p(decay), ws_ptr, ws_bytes, gating_c,
             omega_thresh, adt_delta, adt_smoothness, adt_eps, B, L, H, D, N, C, int(pos0), int(segs),
-            _dtype_code(k), _stream()), "scan_summary_fwd")
+            _dtype_code(k), int(flags) & FP32_DECAY, _stream()), "scan_summary_fwd")
     return carry, decay
 
 
@@ -638,7 +640,7 @@ def scan_fused_long(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_sc
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
     if ev: ev[0].record()
     carry, decay = scan_summary(seg(k), seg(v), seg(gate_raw), log_dt_scale, rope_freqs, *consts, n_heads, N, C,
-                                pos0=base, segs=S)
+                                pos0=base, segs=S, flags=flags)
     if ev: ev[1].record()
     if world > 1:
         # this rank's piece as one summary, exchanged with the other ranks (one small all-gather)

@@ -185,6 +185,11 @@ CDSSM_API int cdssm_b200_conv1d_silu_step(const void* x, int64_t x_row_stride, v
                                       D = C in {64, 128}, H a multiple of 4 and no tail_state):
                                       CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
 
+#define CDSSM_SCAN_FP32_DECAY 4096  /* NOT the reference's arithmetic: the transition A_bar keeps float32 precision
+                                      between the dynamics and the scan.  The reference stores it as bfloat16
+                                      (dynamics_fused.cu:117-125), which puts |a_t| above 1 by rounding for slowly
+                                      rotating heads; its carry (inter_chunk_scan.cu:73-83, decay only) then grows
+                                      exponentially and overflows float32 after a few 1e5 tokens.  Same speed. */
 #define CDSSM_SCAN_TEST_WITHHOLD 2048 /* self-test of the bounded device-side waits (tensor-core passes only): the
                                       producer warp issues no load and no UMMA, so the first wait of every
                                       compute warp runs out after the wait limit, the kernels unwind and set
@@ -232,7 +237,8 @@ CDSSM_API int cdssm_b200_scan_fused_fwd(const void* q, const void* k, const void
  * consecutive segments of B/segs longer sequences: row b starts at position pos0 + (b % segs) * L.
  * Both take the workspace of cdssm_b200_scan_fused_workspace_bytes(B, L, H, D, N, C); the summary
  * leaves its per-chunk results there, and a following fused call on the same inputs and workspace may
- * pass CDSSM_SCAN_REUSE_LOCAL to skip recomputing them.
+ * pass CDSSM_SCAN_REUSE_LOCAL to skip recomputing them.  flags of the summary: 0 or CDSSM_SCAN_FP32_DECAY
+ * (which the fused call that follows must then carry as well).
  * No reference counterpart (the reference is single-GPU and scans a sequence in one piece). */
 CDSSM_API int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const void* gate_raw,
                                           const float* log_dt_scale, const float* rope_freqs,
@@ -240,7 +246,7 @@ CDSSM_API int cdssm_b200_scan_summary_fwd(const void* k, const void* v, const vo
                                           void* workspace, size_t workspace_bytes, float gating_c,
                                           float omega_thresh, float adt_delta, float adt_smoothness,
                                           float adt_eps, int B, int L, int H, int D, int N, int C, int pos0,
-                                          int segs, int dtype, void* stream);
+                                          int segs, int dtype, int flags, void* stream);
 CDSSM_API int cdssm_b200_scan_fused_segmented_fwd(const void* q, const void* k, const void* v,
                                                   const void* gate_raw, const float* log_dt_scale,
                                                   const float* rope_freqs, const float* h0, void* y,

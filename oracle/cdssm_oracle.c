@@ -16,6 +16,10 @@
  *   2  per-token state stores: local_h, cum_A, corrections, Y = local_h + correction, shortcut
  *   4  per-chunk carry: cum_A and local_h of the last step of a chunk, chunk_states
  *   8  outputs: the read-out and its sel_C product
+ *  16  modifier (not a reference behaviour): A_bar is NOT rounded although bit 1 is set - the transition stays
+ *      float32 between the dynamics and the scan.  The reference's bfloat16 A_bar puts |a| above 1 by rounding
+ *      for slowly rotating heads, and its carry (inter_chunk_scan.cu:73-83: decay only, no erasure) then grows
+ *      without bound over some 1e5 tokens; this bit states the same algorithm without that growth.
  * 15 is the reference as it runs (everything bfloat16 between kernels); 0 is the fp32
  * statement of the same algorithm; 13 is "bfloat16 inputs and outputs, fp32 state".
  * Transcendentals use libm, the reference uses --use_fast_math intrinsics: results agree to
@@ -45,6 +49,7 @@ static inline float rnd(float x, int on) { return on ? bf16r(x) : x; }
 #define R_STATE 2
 #define R_CARRY 4
 #define R_OUT 8
+#define R_KEEP_A 16
 
 float orc_bf16_round(float x) { return bf16r(x); }
 
@@ -98,8 +103,8 @@ void orc_dynamics(const float* gate_raw, const float* log_dt_scale, const float*
                     float den2 = fmaf(1.0f + ta, 1.0f + ta, tw * tw);
                     float eig = fmaxf(numer / (den2 + ORC_EPS), 1e-8f);
                     float scale = powf(eig, (gating_c * r_gate - 1.0f) / 2.0f);
-                    A_bar[blh * N + 2 * j] = rnd(mu_re * scale, round_bf16 & R_IN);
-                    A_bar[blh * N + 2 * j + 1] = rnd(-mu_im * scale, round_bf16 & R_IN);
+                    A_bar[blh * N + 2 * j] = rnd(mu_re * scale, (round_bf16 & R_IN) && !(round_bf16 & R_KEEP_A));
+                    A_bar[blh * N + 2 * j + 1] = rnd(-mu_im * scale, (round_bf16 & R_IN) && !(round_bf16 & R_KEEP_A));
                     float eff = powf(eig, gating_c * r_gate);
                     float vp = fminf(sqrtf(fmaxf(1.0f - eff, ORC_EPS)), 1.0f);
                     vp_scale[blh * NH + j] = rnd(vp, round_bf16 & R_IN);

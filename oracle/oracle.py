@@ -17,7 +17,7 @@ _LIB = None
 __all__ = ["build", "lib", "bf16_round", "derive_constants", "dynamics", "normalize_kq",
            "intra_chunk", "inter_chunk", "exact_correction", "conv1d_silu", "scan_reference",
            "scan_recurrent", "make_inputs", "set_threads", "rope_freqs_default", "ROUND_NONE", "ROUND_INPUTS", "ROUND_STATE",
-           "ROUND_CARRY", "ROUND_OUTPUTS", "ROUND_REFERENCE", "ROUND_FP32_STATE"]
+           "ROUND_CARRY", "ROUND_OUTPUTS", "ROUND_REFERENCE", "ROUND_FP32_STATE", "ROUND_KEEP_DECAY"]
 
 
 def build(force=False):
@@ -50,6 +50,7 @@ def _cf(x):
 ROUND_NONE, ROUND_INPUTS, ROUND_STATE, ROUND_CARRY, ROUND_OUTPUTS = 0, 1, 2, 4, 8
 ROUND_REFERENCE = 15          # the reference as it runs
 ROUND_FP32_STATE = 13         # bfloat16 inputs/outputs/carry, fp32 per-token state
+ROUND_KEEP_DECAY = 16         # modifier: A_bar stays float32 (not a reference behaviour; see cdssm_oracle.c)
 
 
 def _mask(round_bf16):

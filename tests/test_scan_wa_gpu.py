@@ -160,3 +160,30 @@ def test_wa_strong_decay(ops, orc, alpha_gate, D):
     assert rel_err(to_np(y), wy13) <= _tol13(D)
     assert rel_err(to_np(y), to_np(ys)) <= BF16_TOL / 2
     assert np.abs(to_np(fin) - to_np(fs)).max() <= 2e-2 * max(np.abs(to_np(fs)).max(), 1e-3)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("path", ["tensor-core", "cuda-core", "segments"])
+def test_float32_transition_option(ops, orc, D, path):
+    """FP32_DECAY keeps A_bar in float32 between the dynamics and the scan (the oracle's ROUND_KEEP_DECAY bit);
+    everything else rounds as before, so the results differ from the reference's only by A_bar's bf16 rounding."""
+    from util import const_args, to_dev
+    B, H, L = 2, 4, 640
+    inp = _inputs(orc, B, H, L, D, seed=21)
+    wy, wf = oracle_scan(orc, inp, N, D, orc.ROUND_FP32_STATE | orc.ROUND_KEEP_DECAY)
+    wy_ref, _ = oracle_scan(orc, inp, N, D, orc.ROUND_FP32_STATE)
+    if path == "segments":
+        d = lambda x: to_dev(x, torch.bfloat16)
+        f = lambda x: to_dev(x, torch.float32)
+        y, fin = ops.scan_fused_long(d(inp["q"]), d(inp["k"]), d(inp["v"]), d(inp["gate_raw"]), f(inp["log_dt_scale"]),
+                                     f(inp["rope_freqs"]), *const_args(inp["consts"]), H, N, D, segments=5, flags=ops.FP32_DECAY)
+    else:
+        extra = ops.TENSOR_CORE_WA if path == "tensor-core" else ops.FORCE_SIMT
+        y, fin = run_fused(ops, inp, torch.bfloat16, N, D, flags=ops.FP32_DECAY | extra)
+    assert ops.scan_fused_status() == 0
+    assert rel_err(to_np(y), wy) <= _tol13(D)
+    assert np.abs(to_np(fin) - wf).max() <= 2e-2 * max(np.abs(wf).max(), 1e-3)
+    # and it is a different arithmetic from the default: the option is not silently ignored
+    y0, _ = run_fused(ops, inp, torch.bfloat16, N, D)
+    assert not torch.equal(y0, y)
+    assert rel_err(to_np(y), wy) < rel_err(to_np(y), wy_ref) or rel_err(wy, wy_ref) < 1e-3
