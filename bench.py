@@ -297,10 +297,21 @@ def lm_arm(args, w, rank, world, local_rank):
             hids = ids.pin_memory()
             last = torch.empty(Bl, cfg.vocab_size, dtype=torch.bfloat16).pin_memory()
 
-            def step():      # end to end: ids from pinned host memory, last-position logits back
-                d = hids.to(dev, non_blocking=True)
-                for b0 in range(0, Bl, 4):
-                    last[b0:b0 + 4].copy_(lm.forward(d[b0:b0 + 4])[:, -1], non_blocking=True)
+            rows = min(Bl, 8)
+            if args.no_graph:
+                def step():      # end to end: ids from pinned host memory, last-position logits back
+                    d = hids.to(dev, non_blocking=True)
+                    for b0 in range(0, Bl, rows):
+                        last[b0:b0 + rows].copy_(lm.forward(d[b0:b0 + rows])[:, -1], non_blocking=True)
+            else:
+                # the forward pass of a (rows, L) slice captured once as a CUDA graph and replayed per slice
+                fgraph, gids, glogits = lm.make_forward_graph(rows, w["L"])
+
+                def step():
+                    for b0 in range(0, Bl, rows):
+                        gids.copy_(hids[b0:b0 + rows], non_blocking=True)
+                        fgraph.replay()
+                        last[b0:b0 + rows].copy_(glogits[:, -1], non_blocking=True)
 
             for _ in range(args.warmup):
                 step()
@@ -311,7 +322,7 @@ def lm_arm(args, w, rank, world, local_rank):
             # layer and slice) on random tensors of the model's shapes, timed alone
             from cdssm_b200 import ops
             Hh, Nn, Dd = cfg.n_heads, cfg.state_dim, cfg.head_dim
-            rb = min(4, Bl)
+            rb = rows
             sq, sk = (torch.randn(rb, w["L"], Hh, Dd, device=dev).bfloat16() for _ in range(2))
             sv = torch.randn(rb, w["L"], Hh, Nn, device=dev).bfloat16()
             sg = torch.randn(rb, w["L"], (Nn + 5) * Hh, device=dev).bfloat16()
@@ -363,7 +374,8 @@ def lm_arm(args, w, rank, world, local_rank):
                 "config": {"workload": f"{args.workload}: CD-SSM LM d_model={cfg.d_model} layers={cfg.n_layers} "
                                        f"heads={H} (reference-derived, d_inner/64) state_dim={N} vocab={cfg.vocab_size} "
                                        f"B={w['B']} L={w['L']}" + (f", {w['decode_steps']}-step greedy decode measured per step"
-                                                                  if decode else ", random token ids"),
+                                                                  if decode else ", random token ids, forward pass of up to 8 rows at a time "
+                                                                  + ("issued eagerly" if args.no_graph else "replayed from one CUDA graph")),
                            "l2": "weights + activations per step exceed the 126 MB L2"},
                 "clocks": clocks.summary(t_begin, t_end),
                 "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -457,6 +469,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--segments", type=int, default=0, help="cfg4: segments per sequence over all GPUs (default: the workload's)")
+    ap.add_argument("--no-graph", action="store_true", help="cfg1_prefill: issue the forward pass eagerly instead of replaying a CUDA graph")
     ap.add_argument("--flags", type=int, default=0, help="scan_fused flags (1 = the CUDA-core kernels instead of the tensor-core passes, 4096 = float32 transition)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]

@@ -39,6 +39,7 @@ SIGNATURES = {
     "cdssm_b200_exact_correction_fwd": (_I, [_P] * 5 + [_I] * 7 + [_P]),
     "cdssm_b200_conv1d_silu_fwd": (_I, [_P] * 4 + [_I] * 4 + [_P]),
     "cdssm_b200_rmsnorm_fwd": (_I, [_P, _P, _P, _c_int64, _I, _F, _I, _P]),
+    "cdssm_b200_groupnorm_stats_floats": (_c_size_t, [_I] * 3),
     "cdssm_b200_groupnorm_stats": (_I, [_P, _P, _I, _I, _I, _I, _F, _I, _P]),
     "cdssm_b200_groupnorm_gate_fwd": (_I, [_P] * 5 + [_c_int64] + [_P] * 3 + [_I] * 4 + [_F, _I, _P]),
     "cdssm_b200_conv1d_silu_step": (_I, [_P, _c_int64, _P, _P, _P, _P, _I, _I, _I, _P]),

@@ -63,43 +63,59 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
 
 // ---------------------------------------------------------------- GroupNorm statistics over a whole sequence
 // The reference normalises (B, d_inner, L): each group's statistics run over its channels AND all positions
-// (block.py:216-222).  One block per (batch row, group); fixed summation order, so the result is deterministic.
+// (block.py:216-222).  Two stages, both with a fixed summation order (deterministic): blocks of di / 8 threads
+// read whole rows (coalesced 16-byte vectors, thread = eight channels) of a tile of positions and leave the
+// tile's (sum, sum of squares) per group; a second, tiny launch adds the tiles in double precision.
+constexpr int kGnTileRows = 32;
+constexpr int kGnMaxTiles = 512;
+static int gn_tiles(int L) {
+    const int t = (L + kGnTileRows - 1) / kGnTileRows;
+    return t < 1 ? 1 : (t > kGnMaxTiles ? kGnMaxTiles : t);
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256)
-groupnorm_stats_kernel(const T* __restrict__ y, float* __restrict__ stats, int L, int di, int groups, float eps) {
-    const int b = blockIdx.x / groups, grp = blockIdx.x % groups;
-    const int cg = di / groups, v8 = cg / 8;
-    const T* base = y + (long long)b * L * di + grp * cg;
-    const long long items = (long long)L * v8;
-    double s = 0.0, q = 0.0;
-    for (long long i = threadIdx.x; i < items; i += 256) {
-        const long long l = i / v8;
-        const int c = (int)(i % v8) * 8;
+__global__ void __launch_bounds__(1024)
+groupnorm_partial_kernel(const T* __restrict__ y, float* __restrict__ partial, int L, int di, int groups, int tiles) {
+    const int b = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+    const int rows = (L + tiles - 1) / tiles;
+    const int l0 = tile * rows, l1 = min(L, l0 + rows);
+    const int cg = di / groups, tpg = cg / 8;
+    const T* base = y + ((long long)b * L) * di + threadIdx.x * 8;
+    float s = 0.f, q = 0.f;
+    for (int l = l0; l < l1; l++) {
         float f[8];
-        Vec8<T>::ld(base + l * di + c, f);
-        float ps = 0.f, pq = 0.f;
+        Vec8<T>::ld(base + (long long)l * di, f);
 #pragma unroll
-        for (int e = 0; e < 8; e++) { ps += f[e]; pq += f[e] * f[e]; }
-        s += ps;
-        q += pq;
+        for (int e = 0; e < 8; e++) { s += f[e]; q = fmaf(f[e], f[e], q); }
     }
-    __shared__ double sh[2][256];
+    __shared__ float sh[2][1024];
     sh[0][threadIdx.x] = s;
     sh[1][threadIdx.x] = q;
     __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) {
-        if ((int)threadIdx.x < o) {
-            sh[0][threadIdx.x] += sh[0][threadIdx.x + o];
-            sh[1][threadIdx.x] += sh[1][threadIdx.x + o];
-        }
-        __syncthreads();
+    if ((int)threadIdx.x < groups) {
+        float ts = 0.f, tq = 0.f;
+        for (int i = 0; i < tpg; i++) { ts += sh[0][threadIdx.x * tpg + i]; tq += sh[1][threadIdx.x * tpg + i]; }
+        float* o = partial + (((long long)b * tiles + tile) * groups + threadIdx.x) * 2;
+        o[0] = ts;
+        o[1] = tq;
     }
-    if (threadIdx.x == 0) {
-        const double n = (double)L * cg, mean = sh[0][0] / n;
-        const double var = fmax(sh[1][0] / n - mean * mean, 0.0);
-        stats[2 * blockIdx.x] = (float)mean;
-        stats[2 * blockIdx.x + 1] = (float)(1.0 / sqrt(var + (double)eps));
+}
+
+__global__ void groupnorm_finalize_kernel(const float* __restrict__ partial, float* __restrict__ stats, int total,
+                                          int L, int cg, int groups, int tiles, float eps) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // (batch row, group)
+    if (i >= total) return;
+    const int b = i / groups, grp = i % groups;
+    double s = 0.0, q = 0.0;
+    for (int t = 0; t < tiles; t++) {
+        const float* p = partial + (((long long)b * tiles + t) * groups + grp) * 2;
+        s += (double)p[0];
+        q += (double)p[1];
     }
+    const double n = (double)L * cg, mean = s / n;
+    const double var = fmax(q / n - mean * mean, 0.0);
+    stats[2 * i] = (float)mean;
+    stats[2 * i + 1] = (float)(1.0 / sqrt(var + (double)eps));
 }
 
 // ---------------------------------------------------------------- GroupNorm + gate + skip
@@ -200,14 +216,25 @@ static int check_gn(int di, int groups) {
     return CDSSM_OK;
 }
 
+extern "C" size_t cdssm_b200_groupnorm_stats_floats(int B, int L, int groups) {
+    if (B <= 0 || L <= 0 || groups <= 0) return 0;
+    return (size_t)B * groups * 2 * (size_t)(1 + gn_tiles(L));
+}
+
 extern "C" int cdssm_b200_groupnorm_stats(const void* y, float* stats, int B, int L, int di, int groups, float eps,
                                           int dtype, void* stream) {
     if (!y || !stats || B < 0 || L < 0) return CDSSM_ERR_BAD_ARG;
     if (int rc = check_gn(di, groups)) return rc;
-    if (!aligned16(y)) return CDSSM_ERR_UNSUPPORTED;
+    if (!aligned16(y) || groups > di / 8) return CDSSM_ERR_UNSUPPORTED;
     if (B == 0 || L == 0) return CDSSM_OK;
-    DISPATCH_DTYPE(dtype, (groupnorm_stats_kernel<T><<<(unsigned)(B * groups), 256, 0, (cudaStream_t)stream>>>(
-                              (const T*)y, stats, L, di, groups, eps)));
+    const int tiles = gn_tiles(L);
+    float* partial = stats + (size_t)B * groups * 2;       // the tiles' sums live behind the results
+    DISPATCH_DTYPE(dtype, (groupnorm_partial_kernel<T><<<(unsigned)(B * tiles), di / 8, 0, (cudaStream_t)stream>>>(
+                              (const T*)y, partial, L, di, groups, tiles)));
+    if (int rc = check_launch()) return rc;
+    const int total = B * groups;
+    groupnorm_finalize_kernel<<<(unsigned)((total + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+        partial, stats, total, L, di / groups, groups, tiles, eps);
     return check_launch();
 }
 

@@ -991,7 +991,7 @@ static int scan_fused_impl(const void* q, const void* k, const void* v, const vo
     if (!(flags & CDSSM_SCAN_FORCE_SIMT) && (wa_asked || wa_ok)) {
         if (!wa_ok) return CDSSM_ERR_UNSUPPORTED;
         cudaStream_t st = (cudaStream_t)stream;
-        const bool tc_local = !(flags & 256), tc_output = !(flags & 512);
+        const bool tc_local = !(flags & CDSSM_SCAN_KEEP_SIMT_LOCAL), tc_output = !(flags & CDSSM_SCAN_KEEP_SIMT_OUTPUT);
         const int withhold = (flags & CDSSM_SCAN_TEST_WITHHOLD) ? 1 : 0;
         const unsigned long long limit = wait_limit_ns();
         void* rec = reinterpret_cast<char*>(a.ws_state) + align256((size_t)a.units * 2 * D * sizeof(float));

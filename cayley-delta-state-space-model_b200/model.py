@@ -165,8 +165,14 @@ class CdssmLM:
         cfg = self.cfg
         B, L, _ = x.shape
         H, N, di = cfg.n_heads, cfg.state_dim, cfg.d_inner
-        proj = F.linear(_rms_norm(x, p.norm_w, cfg.eps_norm), p.w_in, p.b_in)
-        z, x_gate, K, V = proj.split([di, di, di, H * N], dim=-1)
+        xn = _rms_norm(x, p.norm_w, cfg.eps_norm)
+        if L > 1:
+            # One product per consumer (row blocks of the in_proj weight are contiguous views): each output is
+            # dense, so neither the conv nor the scan has to copy a column slice of a wide projection first.
+            z, x_gate, K, V = (F.linear(xn, p.w_in[a:b], p.b_in[a:b]) for a, b in
+                               ((0, di), (di, 2 * di), (2 * di, 3 * di), (3 * di, 3 * di + H * N)))
+        else:
+            z, x_gate, K, V = F.linear(xn, p.w_in, p.b_in).split([di, di, di, H * N], dim=-1)
         K = K.reshape(B, L, H, cfg.head_dim)
         V = V.reshape(B, L, H, N)
         if v_first is None:
@@ -176,7 +182,7 @@ class CdssmLM:
             V = torch.lerp(v_first, V, nu[None, None, :, None])
         decoding = cache is not None and "state" in cache     # a populated cache: one-token step
         if not decoding:
-            x_conv = ops.CUDAConv1dSiLUOp.apply(x_gate.contiguous(), p.conv_w, p.conv_b)
+            x_conv = ops.CUDAConv1dSiLUOp.apply(x_gate, p.conv_w, p.conv_b)
             if cache is not None:               # last three inputs of the causal 4-tap conv
                 hist = torch.zeros(B, 3, di, device=x.device, dtype=x.dtype)
                 n = min(3, L)
@@ -262,6 +268,24 @@ class CdssmLM:
     def position(cache):
         """Number of tokens the cache has seen (reads the device counter if a decode graph owns it)."""
         return int(cache["pos_dev"].item()) if "pos_dev" in cache else int(cache["pos"])
+
+    def make_forward_graph(self, batch, length, scan_flags=0):
+        """Capture forward() for a fixed (batch, length) as one CUDA graph: a prefill of a few thousand tokens is
+        some 200 short launches per pass and otherwise bound by the host that issues them.  Returns
+        (graph, ids, logits): write token ids into ``ids`` (batch, length), ``graph.replay()``, read ``logits``
+        (batch, length, vocab).  The scan workspace belongs to the capture stream and stays alive with the graph."""
+        dev = self.device
+        ids = torch.zeros(batch, length, dtype=torch.int64, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):               # warm-up outside capture: workspaces, lazy library handles
+            for _ in range(2):
+                self.forward(ids, scan_flags)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            logits = self.forward(ids, scan_flags)
+        return graph, ids, logits
 
     def make_decode_graph(self, cache, batch):
         """Capture one greedy decode step as a CUDA graph: static token buffer in, next tokens out,

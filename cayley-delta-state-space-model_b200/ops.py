@@ -297,6 +297,7 @@ FORCE_SIMT = 1
 REUSE_LOCAL = 8
 EXACT = 32
 TENSOR_CORE_WA = 128
+KEEP_SIMT_LOCAL, KEEP_SIMT_OUTPUT = 256, 512   # tests: one tensor-core pass at a time
 TEST_WITHHOLD = 2048   # self-test of the bounded waits: see include/cdssm_b200.h
 FP32_DECAY = 4096      # keep the transition A_bar in float32 (NOT the reference's arithmetic): the reference's
 #                        bfloat16 A_bar lets its carry grow without bound over some 1e5 tokens, see the header
@@ -535,7 +536,8 @@ def groupnorm_gate(y: Tensor, gn_weight: Tensor, gn_bias: Tensor, z: Tensor, ski
     with torch.cuda.device(y.device):
         stats = None
         if not per_token:
-            stats = torch.empty(B, groups, 2, dtype=torch.float32, device=y.device)
+            n_stats = int(_lib.lib().cdssm_b200_groupnorm_stats_floats(B, L, int(groups)))
+            stats = torch.empty(n_stats, dtype=torch.float32, device=y.device)   # results first, then scratch
             check(_lib.lib().cdssm_b200_groupnorm_stats(_p(y), _p(stats), B, L, di, int(groups), float(eps),
                                                         _dtype_code(y), _stream()), "groupnorm_stats")
         check(_lib.lib().cdssm_b200_groupnorm_gate_fwd(_p(y), _p(stats), _p(gw), _p(gb), _p(z), zs, _p(sk), _p(xc),

@@ -149,7 +149,10 @@ CDSSM_API int cdssm_b200_rmsnorm_fwd(const void* x, const void* weight, void* ou
                                      int dtype, void* stream);
 
 /* GroupNorm statistics of y (B,L,di) taken over each group's channels and ALL L positions, as the reference's
- * group_norm on (B, d_inner, L) does (cdssm/models/block.py:216-222): stats (B,groups,2) float32 = mean, rstd. */
+ * group_norm on (B, d_inner, L) does (cdssm/models/block.py:216-222): the first B*groups*2 floats of stats are
+ * (mean, rstd) per (batch row, group); the buffer must hold cdssm_b200_groupnorm_stats_floats(B, L, groups) floats
+ * (the rest is scratch for the per-tile sums of the two-stage, deterministic reduction). */
+CDSSM_API size_t cdssm_b200_groupnorm_stats_floats(int B, int L, int groups);
 CDSSM_API int cdssm_b200_groupnorm_stats(const void* y, float* stats, int B, int L, int di, int groups, float eps,
                                          int dtype, void* stream);
 
@@ -185,6 +188,9 @@ CDSSM_API int cdssm_b200_conv1d_silu_step(const void* x, int64_t x_row_stride, v
                                       D = C in {64, 128}, H a multiple of 4 and no tail_state):
                                       CDSSM_ERR_UNSUPPORTED instead of the CUDA-core kernels otherwise */
 
+#define CDSSM_SCAN_KEEP_SIMT_LOCAL 256  /* tests: with the tensor-core passes, keep the CUDA-core LOCAL pass ... */
+#define CDSSM_SCAN_KEEP_SIMT_OUTPUT 512 /* ... or the CUDA-core OUTPUT pass, so that each tensor-core pass is also
+                                      checked on its own against the other implementation */
 #define CDSSM_SCAN_FP32_DECAY 4096  /* NOT the reference's arithmetic: the transition A_bar keeps float32 precision
                                       between the dynamics and the scan.  The reference stores it as bfloat16
                                       (dynamics_fused.cu:117-125), which puts |a_t| above 1 by rounding for slowly

@@ -104,3 +104,18 @@ def test_forward_is_deterministic_and_batch_independent(lm):
     assert torch.equal(a, b)
     c = lm.forward(ids[1:3])
     assert (c.float() - a[1:3].float()).abs().max() <= 2e-2 * a.float().abs().max()
+
+
+def test_graph_replayed_forward_equals_eager_forward(lm):
+    """forward() captured as one CUDA graph (static ids in, logits out) and replayed on new token ids: the same
+    bits as the eager pass, twice in a row (nothing in the graph depends on state of an earlier replay)."""
+    B, L = 2, 200                                  # head_dim 64, 4 heads: the tensor-core scan passes
+    graph, ids_buf, logits = lm.make_forward_graph(B, L)
+    g = torch.Generator().manual_seed(11)
+    for _ in range(2):
+        ids = torch.randint(0, lm.cfg.vocab_size, (B, L), generator=g).cuda()
+        want = lm.forward(ids)
+        ids_buf.copy_(ids)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(logits, want)
