@@ -110,6 +110,16 @@ class CdssmBlockParams:
         self.shortcut_scale = 0.0
 
 
+    def residual_mix(self, dtype):
+        """sigmoid(v_residual_gate) in the activation dtype (block.py:167-171), computed once per value of the
+        parameter instead of two small kernels per layer and token."""
+        g = self.v_residual_gate
+        key = (g.data_ptr(), g._version, dtype)
+        if getattr(self, "_mix_key", None) != key:
+            self._mix = torch.sigmoid(g).to(dtype)[None, None, :, None]
+            self._mix_key = key
+        return self._mix
+
     def load_reference(self, sd, prefix, device, dtype):
         """Take this block's weights from a reference state dict (parameter names of
         cdssm/models/block.py:35-88 under `prefix`, e.g. "blocks.3.")."""
@@ -178,8 +188,7 @@ class CdssmLM:
         if v_first is None:
             v_first = V
         else:                                   # value residual across layers (block.py:167-171)
-            nu = torch.sigmoid(p.v_residual_gate).to(V.dtype)
-            V = torch.lerp(v_first, V, nu[None, None, :, None])
+            V = torch.lerp(v_first, V, p.residual_mix(V.dtype))
         decoding = cache is not None and "state" in cache     # a populated cache: one-token step
         if not decoding:
             x_conv = ops.CUDAConv1dSiLUOp.apply(x_gate, p.conv_w, p.conv_b)
@@ -220,7 +229,8 @@ class CdssmLM:
                 y = F.group_norm(y.float().transpose(1, 2), cfg.ssm_norm_groups, p.gn_w.float(), p.gn_b.float(),
                                  1e-5).to(x.dtype).transpose(1, 2)
             y = y * F.silu(z) + p.D * x_conv
-        return x + F.linear(y, p.w_out), v_first
+        # the residual add rides in the product's epilogue
+        return torch.addmm(x.reshape(B * L, -1), y.reshape(B * L, di), p.w_out.t()).reshape(B, L, -1), v_first
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()
