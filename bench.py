@@ -438,6 +438,11 @@ def decode_kernel_arm(args, w, local_rank):
         t0 = time.time()
         us = replayed(lambda s: ops.decode_step(s, q, k, v, gate, lds, rope, *consts, H, N, 4096, out=y), reps)
         floor_us = replayed(lambda s: s.mul_(1.0), reps)
+        # the step that reproduces the reference's chunked scan: local state and correction per (batch, head) are
+        # read and written every token (the carry and the chunk decay only change at chunk boundaries)
+        rstates = {id(s): ops.reference_decode_state(s) for s in states}
+        ref_us = replayed(lambda s: ops.decode_step_reference(rstates[id(s)], q, k, v, gate, lds, rope, *consts, H, N,
+                                                              D, 4096 + 17, out=y), reps)
         t1 = time.time()
     per_bh = 2 * N * D * 4 + 2 * D * 2 + (3 * N + 5) * 2
     abytes = B * H * per_bh
@@ -454,7 +459,11 @@ def decode_kernel_arm(args, w, local_rank):
                          "traffic": None, "peak_kind": peak_kind, "kernel": "decode_step_kernel<bf16, 8>",
                          "algorithmic_bytes_per_launch": abytes},
             "floor": {"us": floor_us, "bytes": 2 * B * H * N * D * 4,
-                      "what": "in-place torch elementwise kernel over the same states in the same replay harness"}}
+                      "what": "in-place torch elementwise kernel over the same states in the same replay harness"},
+            "reference_compatible_step": {
+                "us": ref_us, "bytes": B * H * (per_bh + 2 * N * D * 4),
+                "frac": B * H * (per_bh + 2 * N * D * 4) / (ref_us * 1e-6) / 1e9 / peak,
+                "what": "decode_step_reference inside a chunk: local state + correction read and written per token"}}
     print(json.dumps(line))
 
 
