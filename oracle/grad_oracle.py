@@ -1,10 +1,12 @@
-"""Gradient oracle for the two memory-bound operators (float64 numpy).
+"""Gradient oracle for the six operators (float64 numpy).
 
-TEST INFRASTRUCTURE ONLY.  ``dynamics_forward`` restates the forward of dynamics_fused.cu:64-139 without any
-rounding; ``dynamics_backward`` restates the chain of dynamics_fused.cu:187-386 (gate sigmoids, per-pair variance
-scale / recurrence gate / Cayley map, adaptive time step, log_dt_scale); ``normalize_backward`` restates
-normalize_kq.cu:118-160.  tests/test_grad_oracle.py checks both backward functions against central finite differences
-of the forward functions, so a kernel that agrees with them agrees with the derivative of the forward.
+TEST INFRASTRUCTURE ONLY.  Forward and backward restatements, without any rounding, of dynamics_fused.cu:64-139 /
+:187-386, normalize_kq.cu:118-160, intra_chunk_scan.cu:100-195 / :268-540, inter_chunk_scan.cu:52-84 / :115-190,
+exact_correction.cu:83-150 / :230-375 (``reference_order=True``: what that kernel computes; False: the derivative of
+its forward) and conv1d_silu.cu.
+Pinned twice: tests/test_grad_oracle.py checks every backward function against central finite differences of its
+forward function, and against tests/golden/ref_backward.npz - the outputs of the reference's own backward kernels
+(compiled unmodified for sm_100, run on a B200 by tests/golden/make_golden_ref.py).
 """
 import numpy as np
 

@@ -92,6 +92,70 @@ def run_reference(ref, case, orc):
     return out
 
 
+def run_reference_backward(ref, orc):
+    """One small case through the reference's BACKWARD kernels (called directly, each fed with the reference's own
+    forward outputs as the saved tensors and a seeded random upstream gradient).  Returns a dict of numpy arrays:
+    inputs, saved forward outputs, upstream gradients, and the reference's gradients, per operator."""
+    import torch
+    B, NC, C, H, N, D = 1, 2, 64, 2, 2, 64
+    g = torch.Generator(device="cuda").manual_seed(31)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    out = {"sizes": np.array([B, NC, C, H, N, D], np.int64)}
+    put = lambda name, t: out.__setitem__(name, bits(t) if t.dtype == torch.bfloat16 else t.detach().float().cpu().numpy())
+    # dynamics
+    L = 40
+    inp = orc.make_inputs(B, H, L, D, N=N, seed=32, bf16=True, context_length=256)
+    gate = torch.from_numpy(inp["gate_raw"]).cuda().bfloat16()
+    lds, rf = torch.from_numpy(inp["log_dt_scale"]).cuda(), torch.from_numpy(inp["rope_freqs"]).cuda()
+    c = inp["consts"]
+    cs_ = (c["gating_c"], c["omega_thresh"], c["adt_delta"], c["adt_smoothness"], c["adt_eps"])
+    ups = [rn(B, L, H, N).bfloat16(), rn(B, L, H, N // 2).bfloat16(), rn(B, L, H).bfloat16(), rn(B, L, H).bfloat16()]
+    gg, gl = ref.dynamics_fused_bwd_cuda(*ups, gate, lds, rf, *cs_, H, N)
+    out["dyn_consts"] = np.array(cs_, np.float64)
+    for n, t in zip(("dyn_gate", "dyn_lds", "dyn_rope", "dyn_uA", "dyn_uvp", "dyn_ubeta", "dyn_uselc", "dyn_ggate", "dyn_glds"),
+                    (gate, lds, rf, *ups, gg, gl)):
+        put(n, t)
+    # normalisation (head_dim 64: the only size the reference kernel is right for)
+    Kq, Qq, gK, gQ = (rn(3, 7, H, D).bfloat16() for _ in range(4))
+    wK, wQ = ref.normalize_kq_bwd_cuda(gK, gQ, Kq, Qq)
+    for n, t in zip(("nrm_K", "nrm_Q", "nrm_uK", "nrm_uQ", "nrm_gK", "nrm_gQ"), (Kq, Qq, gK, gQ, wK, wQ)):
+        put(n, t)
+    # intra-chunk scan
+    A = (rn(B * NC, C, H, N) * 0.4).bfloat16()
+    K = (rn(B * NC, C, H, D) / 8).bfloat16()
+    V, be = rn(B * NC, C, H, N).bfloat16(), torch.rand(B * NC, C, H, generator=g, device="cuda").bfloat16()
+    lh, cA = ref.intra_chunk_scan_fwd_cuda(A, K, V, be, N)
+    u1, u2 = rn(*lh.shape).bfloat16(), rn(*cA.shape).bfloat16()
+    gi = ref.intra_chunk_scan_bwd_cuda(u1, u2, A, K, V, be, lh, cA, N)
+    for n, t in zip(("A", "K", "V", "beta", "local_h", "cum_A", "intra_ulh", "intra_ucA", "intra_gA", "intra_gK",
+                     "intra_gV", "intra_gbeta"), (A, K, V, be, lh, cA, u1, u2, *gi)):
+        put(n, t)
+    # inter-chunk carry
+    tot, fin = (rn(B, NC + 2, H, N) * 0.4).bfloat16(), rn(B, NC + 2, H, N, D).bfloat16()
+    cs = ref.inter_chunk_scan_fwd_cuda(tot, fin, N)
+    up = rn(*cs.shape).bfloat16()
+    wA, wH = ref.inter_chunk_scan_bwd_cuda(up, tot, cs, N)
+    for n, t in zip(("inter_tot", "inter_fin", "inter_states", "inter_u", "inter_gA", "inter_gH"), (tot, fin, cs, up, wA, wH)):
+        put(n, t)
+    # correction
+    A5, K5, b5 = A.view(B, NC, C, H, N), K.view(B, NC, C, H, D), be.view(B, NC, C, H)
+    st = rn(B, NC, H, N, D).bfloat16()
+    corr = ref.exact_correction_fwd_cuda(A5, K5, b5, st, N)
+    upc = rn(*corr.shape).bfloat16()
+    gc = ref.exact_correction_bwd_cuda(upc, A5, K5, b5, st, corr, N)
+    for n, t in zip(("corr_states", "corr_out", "corr_u", "corr_gA", "corr_gK", "corr_gbeta", "corr_gstates"),
+                    (st, corr, upc, *gc)):
+        put(n, t)
+    # conv
+    x, w4 = rn(2, 37, 64).bfloat16(), (rn(64, 1, 4) / 2).bfloat16()
+    bias, upx = (rn(64) / 5).bfloat16(), rn(2, 37, 64).bfloat16()
+    gx = ref.conv1d_silu_bwd_cuda(x, w4, bias, upx)
+    for n, t in zip(("conv_x", "conv_w", "conv_b", "conv_u", "conv_gx", "conv_gw", "conv_gb"), (x, w4, bias, upx, *gx)):
+        put(n, t)
+    torch.cuda.synchronize()
+    return out
+
+
 def _consts(g):
     c = g["consts"]
     return dict(gating_c=float(c[0]), omega_thresh=float(c[1]), adt_delta=float(c[2]),

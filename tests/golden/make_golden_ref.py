@@ -4,7 +4,7 @@ sources are mounted):
 
     python tests/golden/make_golden_ref.py [outdir]
 
-Writes ref_<case>.npz files (default: ./golden_out/); copy them into tests/golden/.
+Writes ref_<case>.npz files and ref_backward.npz (the reference's backward kernels on one small case) (default: ./golden_out/); copy them into tests/golden/.
 """
 import os
 import sys
@@ -20,7 +20,7 @@ sys.path.insert(0, os.path.dirname(HERE))
 def main():
     import oracle
     from oracle.build_ref import load_ref
-    from golden.golden_cases import CASES, run_reference
+    from golden.golden_cases import CASES, run_reference, run_reference_backward
     ref = load_ref()
     if ref is None:
         raise SystemExit("oracle/_ref/cdssm_ref_C.so not built")
@@ -32,6 +32,9 @@ def main():
         np.savez_compressed(path, **res)
         print(name, {k: v.shape for k, v in res.items() if hasattr(v, "shape") and v.ndim > 1},
               os.path.getsize(path), "bytes")
+    path = os.path.join(out, "ref_backward.npz")
+    np.savez_compressed(path, **run_reference_backward(ref, oracle))
+    print("backward", os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 
 from oracle import grad_oracle as go
+from util import rel_err
 
 
 def _case(orc, B, H, L, N, seed):
@@ -140,3 +141,48 @@ def test_conv_backward_is_the_derivative(orc):
     _close(gx, _fd(lambda t: float((go.conv_forward(t, w, b) * up).sum()), x))
     _close(gw, _fd(lambda t: float((go.conv_forward(x, t, b) * up).sum()), w))
     _close(gb, _fd(lambda t: float((go.conv_forward(x, w, t) * up).sum()), b))
+
+
+def test_gradient_oracle_matches_the_reference_backward_kernels():
+    """The pin of the gradient oracle: tests/golden/ref_backward.npz holds what the reference's own backward kernels
+    (compiled unmodified for sm_100, run on a B200 by tests/golden/make_golden_ref.py) returned for seeded inputs,
+    their own forward outputs as saved tensors and seeded upstream gradients.  The float64 oracle reproduces them
+    within the bfloat16 storage of the reference's outputs - the correction backward only in ``reference_order``
+    (the reference adds the upstream gradient before the step it belongs behind, and its grad_beta is head_dim
+    times the derivative)."""
+    import os
+    from golden.golden_cases import unbits
+    from oracle import grad_oracle as go
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_backward.npz"))
+    f = lambda n: unbits(g[n]).astype(np.float64) if g[n].dtype == np.uint16 else g[n].astype(np.float64)
+    B, NC, C, H, N, D = (int(x) for x in g["sizes"])
+    close = lambda got, want, tol, what: rel_err(got, want) <= tol or pytest.fail(f"{what}: {rel_err(got, want):.3g} > {tol}")
+    # dynamics
+    c = dict(zip(("gating_c", "omega_thresh", "adt_delta", "adt_smoothness", "adt_eps"), g["dyn_consts"]))
+    gg, gl = go.dynamics_backward(f("dyn_uA"), f("dyn_uvp"), f("dyn_ubeta"), f("dyn_uselc"), f("dyn_gate"), f("dyn_lds"),
+                                  f("dyn_rope"), c, H, N)
+    close(gg, f("dyn_ggate"), 2e-2, "dynamics grad_gate_raw")
+    close(gl, f("dyn_glds"), 2e-2, "dynamics grad_log_dt_scale")
+    # normalisation
+    close(go.normalize_backward(f("nrm_uK"), f("nrm_K")), f("nrm_gK"), 1e-2, "normalize grad_K")
+    close(go.normalize_backward(f("nrm_uQ"), f("nrm_Q")), f("nrm_gQ"), 1e-2, "normalize grad_Q")
+    # intra-chunk scan
+    got = go.intra_backward(f("intra_ulh"), f("intra_ucA"), f("A"), f("K"), f("V"), f("beta"), f("local_h"), f("cum_A"))
+    for x, n in zip(got, ("intra_gA", "intra_gK", "intra_gV", "intra_gbeta")):
+        close(x, f(n), 2e-2, n)
+    # inter-chunk carry
+    gA, gH = go.inter_backward(f("inter_u"), f("inter_tot"), f("inter_states"))
+    close(gA, f("inter_gA"), 2e-2, "inter grad_total_A")
+    close(gH, f("inter_gH"), 2e-2, "inter grad_final_h")
+    # correction: the reference's order (and not the derivative of its forward)
+    A5, K5, b5 = f("A").reshape(B, NC, C, H, N), f("K").reshape(B, NC, C, H, D), f("beta").reshape(B, NC, C, H)
+    got = go.correction_backward(f("corr_u"), A5, K5, b5, f("corr_states"), f("corr_out"), reference_order=True)
+    for x, n in zip(got, ("corr_gA", "corr_gK", "corr_gbeta", "corr_gstates")):
+        close(x, f(n), 2e-2, n)
+    true = go.correction_backward(f("corr_u"), A5, K5, b5, f("corr_states"), f("corr_out"), reference_order=False)
+    assert rel_err(true[2] * D, f("corr_gbeta")) > 5e-2          # the true derivative is a different vector
+    # conv
+    gx, gw, gb = go.conv_backward(f("conv_u"), f("conv_x"), f("conv_w").reshape(-1, 4), f("conv_b"))
+    close(gx, f("conv_gx"), 2e-2, "conv grad_x")
+    close(np.asarray(gw).reshape(-1), f("conv_gw").reshape(-1), 2e-2, "conv grad_weight")
+    close(gb, f("conv_gb"), 2e-2, "conv grad_bias")
