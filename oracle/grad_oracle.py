@@ -5,7 +5,7 @@ TEST INFRASTRUCTURE ONLY.  Forward and backward restatements, without any roundi
 exact_correction.cu:83-150 / :230-375 (``reference_order=True``: what that kernel computes; False: the derivative of
 its forward) and conv1d_silu.cu.
 Pinned twice: tests/test_grad_oracle.py checks every backward function against central finite differences of its
-forward function, and against tests/golden/ref_backward.npz - the outputs of the reference's own backward kernels
+forward function, and against tests/golden/bwd_ref.npz - the outputs of the reference's own backward kernels
 (compiled unmodified for sm_100, run on a B200 by tests/golden/make_golden_ref.py).
 """
 import numpy as np

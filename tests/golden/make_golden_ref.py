@@ -4,7 +4,7 @@ sources are mounted):
 
     python tests/golden/make_golden_ref.py [outdir]
 
-Writes ref_<case>.npz files and ref_backward.npz (the reference's backward kernels on one small case) (default: ./golden_out/); copy them into tests/golden/.
+Writes ref_<case>.npz files and bwd_ref.npz (the reference's backward kernels on one small case) (default: ./golden_out/); copy them into tests/golden/.
 """
 import os
 import sys
@@ -32,7 +32,7 @@ def main():
         np.savez_compressed(path, **res)
         print(name, {k: v.shape for k, v in res.items() if hasattr(v, "shape") and v.ndim > 1},
               os.path.getsize(path), "bytes")
-    path = os.path.join(out, "ref_backward.npz")
+    path = os.path.join(out, "bwd_ref.npz")
     np.savez_compressed(path, **run_reference_backward(ref, oracle))
     print("backward", os.path.getsize(path), "bytes")
 

@@ -144,7 +144,7 @@ def test_conv_backward_is_the_derivative(orc):
 
 
 def test_gradient_oracle_matches_the_reference_backward_kernels():
-    """The pin of the gradient oracle: tests/golden/ref_backward.npz holds what the reference's own backward kernels
+    """The pin of the gradient oracle: tests/golden/bwd_ref.npz holds what the reference's own backward kernels
     (compiled unmodified for sm_100, run on a B200 by tests/golden/make_golden_ref.py) returned for seeded inputs,
     their own forward outputs as saved tensors and seeded upstream gradients.  The float64 oracle reproduces them
     within the bfloat16 storage of the reference's outputs - the correction backward only in ``reference_order``
@@ -153,7 +153,7 @@ def test_gradient_oracle_matches_the_reference_backward_kernels():
     import os
     from golden.golden_cases import unbits
     from oracle import grad_oracle as go
-    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_backward.npz"))
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bwd_ref.npz"))
     f = lambda n: unbits(g[n]).astype(np.float64) if g[n].dtype == np.uint16 else g[n].astype(np.float64)
     B, NC, C, H, N, D = (int(x) for x in g["sizes"])
     close = lambda got, want, tol, what: rel_err(got, want) <= tol or pytest.fail(f"{what}: {rel_err(got, want):.3g} > {tol}")
