@@ -61,6 +61,38 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restri
     }
 }
 
+// Few rows (a decode step: one row per sequence): one block per row, so that a row's loads are spread over 256
+// threads instead of one warp's dependent loop.  Same arithmetic; the sum of squares is reduced in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_row_block_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, int d, float eps) {
+    const T* xr = x + (long long)blockIdx.x * d;
+    T* orow = out + (long long)blockIdx.x * d;
+    __shared__ float sh[8];
+    float ss = 0.f;
+    for (int c = threadIdx.x * 8; c < d; c += 2048) {
+        float f[8];
+        Vec8<T>::ld(xr + c, f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += f[e] * f[e];
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += sh[i];
+    const float rms = rsqrtf(tot / (float)d + eps);
+    for (int c = threadIdx.x * 8; c < d; c += 2048) {
+        float f[8], g[8];
+        Vec8<T>::ld(xr + c, f);
+        Vec8<T>::ld(w + c, g);
+#pragma unroll
+        for (int e = 0; e < 8; e++) f[e] = IO<T>::rnd(f[e] * rms) * g[e];
+        Vec8<T>::st(orow + c, f);
+    }
+}
+
 // ---------------------------------------------------------------- GroupNorm statistics over a whole sequence
 // The reference normalises (B, d_inner, L): each group's statistics run over its channels AND all positions
 // (block.py:216-222).  Two stages, both with a fixed summation order (deterministic): blocks of di / 8 threads
@@ -188,6 +220,39 @@ conv1d_silu_step_kernel(const T* __restrict__ x, long long x_row_stride, T* __re
     IO<T>::st(h + 2 * Dm, x3);
 }
 
+// Eight channels per thread (16-byte accesses of x, the history rows and the output; the 4 taps of a channel are
+// 8 contiguous bytes of the (Dm,1,4) weight).
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv1d_silu_step_vec_kernel(const T* __restrict__ x, long long x_row_stride, T* __restrict__ hist,
+                            const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ out, int B, int Dm) {
+    const int v8 = Dm / 8;
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (long long)B * v8) return;
+    const int d = (int)(idx % v8) * 8;
+    const long long b = idx / v8;
+    T* h = hist + b * 3 * Dm + d;
+    float x0[8], x1[8], x2[8], x3[8], bi[8], wa[8], wb[8], wc[8], wd[8], y[8];
+    Vec8<T>::ld(h, x0);
+    Vec8<T>::ld(h + Dm, x1);
+    Vec8<T>::ld(h + 2 * Dm, x2);
+    Vec8<T>::ld(x + b * x_row_stride + d, x3);
+    Vec8<T>::ld(bias + d, bi);
+    Vec8<T>::ld(w + d * 4, wa);          // taps of channels d, d + 1
+    Vec8<T>::ld(w + d * 4 + 8, wb);      // d + 2, d + 3
+    Vec8<T>::ld(w + d * 4 + 16, wc);
+    Vec8<T>::ld(w + d * 4 + 24, wd);
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float* ww = (e < 2 ? wa : e < 4 ? wb : e < 6 ? wc : wd) + (e & 1) * 4;
+        y[e] = siluf_<IO<T>::kBf16>(ww[0] * x0[e] + ww[1] * x1[e] + ww[2] * x2[e] + ww[3] * x3[e] + bi[e]);
+    }
+    Vec8<T>::st(out + b * Dm + d, y);
+    Vec8<T>::st(h, x1);
+    Vec8<T>::st(h + Dm, x2);
+    Vec8<T>::st(h + 2 * Dm, x3);
+}
+
 }  // namespace cdssm
 
 using namespace cdssm;
@@ -204,6 +269,11 @@ extern "C" int cdssm_b200_rmsnorm_fwd(const void* x, const void* weight, void* o
     if (!x || !weight || !out || rows < 0 || d <= 0) return CDSSM_ERR_BAD_ARG;
     if (d % 8 || !aligned16(x) || !aligned16(weight) || !aligned16(out)) return CDSSM_ERR_UNSUPPORTED;
     if (rows == 0) return CDSSM_OK;
+    if (rows <= 2048) {   // one block per row
+        DISPATCH_DTYPE(dtype, (rmsnorm_row_block_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+                                  (const T*)x, (const T*)weight, (T*)out, d, eps)));
+        return check_launch();
+    }
     const unsigned blocks = (unsigned)((rows + 7) / 8);
     DISPATCH_DTYPE(dtype, (rmsnorm_fwd_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(
                               (const T*)x, (const T*)weight, (T*)out, rows, d, eps)));
@@ -261,6 +331,14 @@ extern "C" int cdssm_b200_conv1d_silu_step(const void* x, int64_t x_row_stride, 
                                            const void* bias, void* out, int B, int Dm, int dtype, void* stream) {
     if (!x || !hist || !weight || !bias || !out || B < 0 || Dm <= 0) return CDSSM_ERR_BAD_ARG;
     if (B == 0) return CDSSM_OK;
+    const size_t es = dtype == CDSSM_F32 ? 4 : 2;
+    if (Dm % 8 == 0 && aligned16(x) && aligned16(hist) && aligned16(weight) && aligned16(bias) && aligned16(out) &&
+        (x_row_stride * es) % 16 == 0) {
+        const long long nv = (long long)B * (Dm / 8);
+        DISPATCH_DTYPE(dtype, (conv1d_silu_step_vec_kernel<T><<<(unsigned)((nv + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                                  (const T*)x, x_row_stride, (T*)hist, (const T*)weight, (const T*)bias, (T*)out, B, Dm)));
+        return check_launch();
+    }
     const long long n = (long long)B * Dm;
     DISPATCH_DTYPE(dtype, (conv1d_silu_step_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                               (const T*)x, x_row_stride, (T*)hist, (const T*)weight, (const T*)bias, (T*)out, B, Dm)));
