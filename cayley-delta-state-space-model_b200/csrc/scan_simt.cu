@@ -606,6 +606,8 @@ struct DecodeArgs {
     float *corr, *carry, *gamma;   // reference-compatible step only: correction, carry (B,H,N,D), chunk decay (B,H,N)
     int C;                         // chunk length of the reference-compatible step
     const void *q, *k, *v, *gate_raw;
+    long long k_stride, v_stride;  // elements between the batch rows of k and v (column slices of a wider projection)
+    const void *v_first, *mix;     // plain step only, or NULL: v <- lerp(v_first, v, mix[head]) (value residual)
     const float *log_dt_scale, *rope_freqs;
     void* y;
     DynConsts dc;
@@ -630,7 +632,7 @@ decode_step_kernel(const DecodeArgs a) {
     const long long bh = b * H + hd;
 
     RowSlice<T, kCols> kraw, qraw;
-    kraw.load(static_cast<const T*>(a.k) + bh * D, g, D, vec);
+    kraw.load(static_cast<const T*>(a.k) + b * a.k_stride + (long long)hd * D, g, D, vec);
     qraw.load(static_cast<const T*>(a.q) + bh * D, g, D, vec);
     float* st = a.state + (bh * a.N + 2 * j) * D;
     float zr[kCols], zi[kCols];
@@ -664,8 +666,16 @@ decode_step_kernel(const DecodeArgs a) {
     a_im = IO<T>::rnd(a_im);
     vp = IO<T>::rnd(vp);
     const float be = IO<T>::rnd(ds.beta), sc = IO<T>::rnd(ds.sel_c);
-    const T* vrow = static_cast<const T*>(a.v) + bh * a.N + 2 * j;
-    const float vr = IO<T>::rnd(IO<T>::ld(vrow) * vp), vi = IO<T>::rnd(IO<T>::ld(vrow + 1) * vp);
+    const T* vrow = static_cast<const T*>(a.v) + b * a.v_stride + (long long)hd * a.N + 2 * j;
+    float v0 = IO<T>::ld(vrow), v1 = IO<T>::ld(vrow + 1);
+    if (a.v_first) {   // value residual across layers (block.py:167-171), rounded like the eager lerp's output
+        const T* f = static_cast<const T*>(a.v_first) + bh * a.N + 2 * j;
+        const float w = IO<T>::ld(static_cast<const T*>(a.mix) + hd), f0 = IO<T>::ld(f), f1 = IO<T>::ld(f + 1);
+        const float d0 = v0 - f0, d1 = v1 - f1;
+        v0 = IO<T>::rnd(fabsf(w) < 0.5f ? f0 + w * d0 : v0 - d0 * (1.f - w));
+        v1 = IO<T>::rnd(fabsf(w) < 0.5f ? f1 + w * d1 : v1 - d1 * (1.f - w));
+    }
+    const float vr = IO<T>::rnd(v0 * vp), vi = IO<T>::rnd(v1 * vp);
 
     float kk[kCols], qq[kCols];
     kraw.get(kk);
@@ -1018,7 +1028,8 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
                             void* y, float gating_c, float omega_thresh, float adt_delta,
                             float adt_smoothness, float adt_eps, float shortcut_scale, int B, int H, int D,
                             int N, int pos, const int* pos_dev, int dtype, void* stream, float* corr = nullptr,
-                            float* carry = nullptr, float* gamma = nullptr, int C = 0) {
+                            float* carry = nullptr, float* gamma = nullptr, int C = 0, long long k_stride = 0,
+                            long long v_stride = 0, const void* v_first = nullptr, const void* mix = nullptr) {
     if (!state || !q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y)
         return CDSSM_ERR_BAD_ARG;
     if (corr && (!carry || !gamma || C <= 0 || (((uintptr_t)corr | (uintptr_t)carry) & 15))) return CDSSM_ERR_BAD_ARG;
@@ -1030,6 +1041,16 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
     DecodeArgs a;
     a.state = state; a.q = q; a.k = k; a.v = v; a.gate_raw = gate_raw;
     a.corr = corr; a.carry = carry; a.gamma = gamma; a.C = C;
+    a.k_stride = k_stride ? k_stride : (long long)H * D;
+    a.v_stride = v_stride ? v_stride : (long long)H * N;
+    a.v_first = v_first; a.mix = mix;
+    {
+        const long long es = dtype == CDSSM_F32 ? 4 : 2;
+        if ((a.k_stride * es) & 15) return CDSSM_ERR_BAD_ARG;                 // 16-byte row loads of k
+        if (a.k_stride < (long long)H * D || a.v_stride < (long long)H * N) return CDSSM_ERR_BAD_ARG;
+        if ((v_first != nullptr) != (mix != nullptr)) return CDSSM_ERR_BAD_ARG;
+        if (corr && (v_first || k_stride || v_stride)) return CDSSM_ERR_UNSUPPORTED;
+    }
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.y = y;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
     a.shortcut_scale = shortcut_scale;
@@ -1175,6 +1196,19 @@ extern "C" int cdssm_b200_decode_step_at(float* state, const void* q, const void
     return decode_step_impl(state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
                             adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, 0, pos_dev,
                             dtype, stream);
+}
+
+extern "C" int cdssm_b200_decode_step_strided(float* state, const void* q, const void* k, int64_t k_row_stride,
+                                              const void* v, int64_t v_row_stride, const void* v_first,
+                                              const void* mix, const void* gate_raw, const float* log_dt_scale,
+                                              const float* rope_freqs, void* y, float gating_c, float omega_thresh,
+                                              float adt_delta, float adt_smoothness, float adt_eps,
+                                              float shortcut_scale, int B, int H, int D, int N, int pos,
+                                              const int* pos_dev, int dtype, void* stream) {
+    if (k_row_stride <= 0 || v_row_stride <= 0) return CDSSM_ERR_BAD_ARG;
+    return decode_step_impl(state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
+                            adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, pos, pos_dev, dtype,
+                            stream, nullptr, nullptr, nullptr, 0, k_row_stride, v_row_stride, v_first, mix);
 }
 
 extern "C" int cdssm_b200_decode_step_reference(float* local_state, float* correction, float* carry, float* chunk_decay,

@@ -185,11 +185,14 @@ class CdssmLM:
             z, x_gate, K, V = F.linear(xn, p.w_in, p.b_in).split([di, di, di, H * N], dim=-1)
         K = K.reshape(B, L, H, cfg.head_dim)
         V = V.reshape(B, L, H, N)
+        decoding = cache is not None and "state" in cache     # a populated cache: one-token step
+        mix = None
         if v_first is None:
-            v_first = V
+            v_first = V.contiguous() if decoding else V     # one small copy per step; the kernels read it densely
+        elif decoding:                          # the decode kernel applies the value residual itself
+            mix = p.residual_mix(V.dtype)
         else:                                   # value residual across layers (block.py:167-171)
             V = torch.lerp(v_first, V, p.residual_mix(V.dtype))
-        decoding = cache is not None and "state" in cache     # a populated cache: one-token step
         if not decoding:
             x_conv = ops.CUDAConv1dSiLUOp.apply(x_gate, p.conv_w, p.conv_b)
             if cache is not None:               # last three inputs of the causal 4-tap conv
@@ -203,8 +206,8 @@ class CdssmLM:
         Q = F.linear(x_conv, p.w_q).reshape(B, L, H, cfg.head_dim)
         if decoding:
             y = ops.decode_step(cache["state"], Q[:, 0], K[:, 0], V[:, 0], gates[:, 0], p.log_dt_scale,
-                                p.rope_freqs, *cfg.dyn_consts, H, N, pos0,
-                                shortcut_scale=p.shortcut_scale).unsqueeze(1)
+                                p.rope_freqs, *cfg.dyn_consts, H, N, pos0, shortcut_scale=p.shortcut_scale,
+                                v_first=None if mix is None else v_first[:, 0], mix=mix).unsqueeze(1)
         elif cache is not None:
             y, _, tail = ops.scan_fused(Q, K, V, gates, p.log_dt_scale, p.rope_freqs, *cfg.dyn_consts, H, N,
                                         cfg.chunk_size, shortcut_scale=p.shortcut_scale, pos0=pos0,

@@ -400,41 +400,54 @@ def scan_fused(q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor, log_dt_scale: 
 def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor,
                 log_dt_scale: Tensor, rope_freqs: Tensor, gating_c: float, omega_thresh: float,
                 adt_delta: float, adt_smoothness: float, adt_eps: float, n_heads: int,
-                state_dim: int, pos: int, *, shortcut_scale: float = 0.0, out: Tensor = None) -> Tensor:
+                state_dim: int, pos: int, *, shortcut_scale: float = 0.0, out: Tensor = None,
+                v_first: Tensor = None, mix: Tensor = None) -> Tensor:
     """One recurrent step for every sequence of a batch; ``state`` (B,H,N,D) float32 is updated
     in place.  q, k: (B,H,D); v: (B,H,N); gate_raw: (B,(N+5)H); returns y (B,H,N).
+    k and v may be column slices of a wider per-token projection (only their batch stride is free).
+    ``v_first`` (B,H,N) with ``mix`` (H): the value residual v <- lerp(v_first, v, mix[head]) of
+    cdssm/models/block.py:167-171 is applied inside the kernel.
 
     The reference has no such step (cdssm/inference/predict.py:53-67 re-runs the full forward
     for every new token); the update is one iteration of intra_chunk_scan.cu:117-167 with the
     gates of dynamics_fused.cu:64-139 at position ``pos``.
     """
     q = _prep(q, name="q")
-    k = _prep(k, dtype=q.dtype, name="k")
-    v = _prep(v, dtype=q.dtype, name="v")
+    B, H, D = q.shape
+    N = int(state_dim)
+
+    def rows(t, inner, name):
+        """(B,H,inner) with contiguous rows; the batch stride may be larger (a slice of a projection)."""
+        if t.is_cuda and t.dtype == q.dtype and tuple(t.shape) == (B, H, inner) and t.stride(2) == 1 and \
+                t.stride(1) == inner and t.stride(0) >= H * inner and \
+                (t.stride(0) * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0:
+            return t
+        return _prep(t, dtype=q.dtype, name=name)
+
+    k, v = rows(k, D, "k"), rows(v, N, "v")
     g = _prep(gate_raw, dtype=q.dtype, name="gate_raw")
     if not state.is_cuda or state.dtype != torch.float32 or not state.is_contiguous():
         raise CdssmError("state must be a contiguous float32 CUDA tensor (B,H,N,D)")
-    B, H, D = q.shape
-    N = int(state_dim)
-    if H != int(n_heads) or tuple(state.shape) != (B, H, N, D) or tuple(v.shape) != (B, H, N) or \
-            tuple(g.shape) != (B, (N + 5) * H):
+    if H != int(n_heads) or tuple(state.shape) != (B, H, N, D) or tuple(k.shape) != (B, H, D) or \
+            tuple(v.shape) != (B, H, N) or tuple(g.shape) != (B, (N + 5) * H):
         raise CdssmError("decode_step: inconsistent shapes")
+    if (v_first is None) != (mix is None):
+        raise CdssmError("decode_step: v_first and mix go together")
+    if v_first is not None:
+        v_first = _prep(v_first, dtype=q.dtype, name="v_first")
+        mix = _prep(mix.reshape(-1), dtype=q.dtype, name="mix")
+        if tuple(v_first.shape) != (B, H, N) or mix.numel() != H:
+            raise CdssmError("decode_step: v_first must be (B,H,N) and mix (H)")
     lds, rf = _f32(log_dt_scale, "log_dt_scale"), _f32(rope_freqs, "rope_freqs")
     y = out if out is not None else torch.empty(B, H, N, dtype=q.dtype, device=q.device)
-    if isinstance(pos, Tensor):      # position in device memory (int32): graph-replayable
-        if pos.dtype != torch.int32 or not pos.is_cuda:
-            raise CdssmError("a tensor position must be an int32 CUDA tensor")
-        with torch.cuda.device(q.device):
-            check(_lib.lib().cdssm_b200_decode_step_at(
-                _p(state), _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh,
-                adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, _p(pos), _dtype_code(q),
-                _stream()), "decode_step_at")
-        return y
+    pos_dev, pos_i = (pos, 0) if isinstance(pos, Tensor) else (None, int(pos))
+    if pos_dev is not None and (pos_dev.dtype != torch.int32 or not pos_dev.is_cuda):
+        raise CdssmError("a tensor position must be an int32 CUDA tensor")   # device memory: graph-replayable
     with torch.cuda.device(q.device):
-        check(_lib.lib().cdssm_b200_decode_step(
-            _p(state), _p(q), _p(k), _p(v), _p(g), _p(lds), _p(rf), _p(y), gating_c, omega_thresh,
-            adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, int(pos), _dtype_code(q),
-            _stream()), "decode_step")
+        check(_lib.lib().cdssm_b200_decode_step_strided(
+            _p(state), _p(q), _p(k), k.stride(0), _p(v), v.stride(0), _p(v_first), _p(mix), _p(g), _p(lds), _p(rf),
+            _p(y), gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, pos_i,
+            _p(pos_dev), _dtype_code(q), _stream()), "decode_step")
     return y
 
 

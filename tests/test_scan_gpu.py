@@ -275,3 +275,25 @@ def test_reference_decode_continues_a_chunk_aligned_prefill(ops, orc):
         pos += 1
     y = torch.stack(ys, 1)
     assert rel_err(to_np(y), to_np(full[:, L0:])) <= BF16_TOL / 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_step_with_projection_slices_and_value_residual(ops, orc, dtype):
+    """k and v as column slices of a wider projection and the value residual folded into the kernel: the same
+    bits as contiguous copies and an eager torch.lerp in front of the plain step."""
+    B, H, D, N = 5, 4, 64, 2
+    g = torch.Generator(device="cuda").manual_seed(8)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda").to(dtype)
+    proj = rn(B, H * D + H * N + 24)                       # [k | v | something else], row width a multiple of 8
+    k, v = proj[:, :H * D].view(B, H, D), proj[:, H * D:H * D + H * N].view(B, H, N)
+    assert not k.is_contiguous()
+    q, gate, v_first = rn(B, H, D), rn(B, (N + 5) * H), rn(B, H, N)
+    mix = torch.sigmoid(torch.randn(H, generator=g, device="cuda") * 2).to(dtype)     # both lerp branches
+    lds, rf = torch.zeros(H, device="cuda"), torch.linspace(0.1, 1.0, H, device="cuda")
+    consts = (3.0, 2 ** -3.5, 0.125, 2 ** -3.5 / 5, 1.0)
+    s0 = torch.randn(B, H, N, D, generator=g, device="cuda") * 0.3
+    s1, s2 = s0.clone(), s0.clone()
+    y1 = ops.decode_step(s1, q, k, v, gate, lds, rf, *consts, H, N, 7, shortcut_scale=0.4, v_first=v_first, mix=mix)
+    vm = torch.lerp(v_first, v.contiguous(), mix[None, :, None])
+    y2 = ops.decode_step(s2, q, k.contiguous(), vm, gate, lds, rf, *consts, H, N, 7, shortcut_scale=0.4)
+    assert torch.equal(y1, y2) and torch.equal(s1, s2)
