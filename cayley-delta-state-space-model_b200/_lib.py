@@ -55,7 +55,7 @@ SIGNATURES = {
     "cdssm_b200_set_wait_limit_ns": (ctypes.c_uint64, [ctypes.c_uint64]),
     "cdssm_b200_selftest_bounded_wait": (_I, [_P, ctypes.c_uint64, _P]),
     "cdssm_b200_decode_step": (_I, [_P] * 8 + [_F] * 6 + [_I] * 6 + [_P]),
-    "cdssm_b200_decode_step_strided": (_I, [_P, _P, _P, _c_int64, _P, _c_int64] + [_P] * 6 + [_F] * 6 + [_I] * 5 + [_P, _I, _P]),
+    "cdssm_b200_decode_step_strided": (_I, [_P, _P, _c_int64, _P, _c_int64, _P, _c_int64, _P, _P, _P, _c_int64] + [_P] * 3 + [_F] * 6 + [_I] * 5 + [_P, _I, _P]),
     "cdssm_b200_decode_step_reference": (_I, [_P] * 11 + [_F] * 6 + [_I] * 6 + [_P, _I, _P]),
     "cdssm_b200_decode_step_at": (_I, [_P] * 8 + [_F] * 6 + [_I] * 4 + [_P, _I, _P]),
 }

@@ -607,6 +607,7 @@ struct DecodeArgs {
     int C;                         // chunk length of the reference-compatible step
     const void *q, *k, *v, *gate_raw;
     long long k_stride, v_stride;  // elements between the batch rows of k and v (column slices of a wider projection)
+    long long q_stride, g_stride;  // the same for q and gate_raw (plain step only)
     const void *v_first, *mix;     // plain step only, or NULL: v <- lerp(v_first, v, mix[head]) (value residual)
     const float *log_dt_scale, *rope_freqs;
     void* y;
@@ -633,7 +634,7 @@ decode_step_kernel(const DecodeArgs a) {
 
     RowSlice<T, kCols> kraw, qraw;
     kraw.load(static_cast<const T*>(a.k) + b * a.k_stride + (long long)hd * D, g, D, vec);
-    qraw.load(static_cast<const T*>(a.q) + bh * D, g, D, vec);
+    qraw.load(static_cast<const T*>(a.q) + b * a.q_stride + (long long)hd * D, g, D, vec);
     float* st = a.state + (bh * a.N + 2 * j) * D;
     float zr[kCols], zi[kCols];
     if (vec) {
@@ -653,7 +654,7 @@ decode_step_kernel(const DecodeArgs a) {
         }
     }
     // dynamics (every lane of the unit computes the same scalars; dynamics_fused.cu:64-139)
-    const T* gr = static_cast<const T*>(a.gate_raw) + b * (long long)((a.N + 5) * H);
+    const T* gr = static_cast<const T*>(a.gate_raw) + b * a.g_stride;
     const T* s5 = gr + a.N * H;
     const float freq = a.rope_freqs[hd], pos = (float)(a.pos_dev ? *a.pos_dev : a.pos);
     DynShared ds = dyn_shared<IO<T>::kBf16>(IO<T>::ld(gr + hd), IO<T>::ld(gr + NH * H + hd), IO<T>::ld(s5 + hd),
@@ -1029,7 +1030,8 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
                             float adt_smoothness, float adt_eps, float shortcut_scale, int B, int H, int D,
                             int N, int pos, const int* pos_dev, int dtype, void* stream, float* corr = nullptr,
                             float* carry = nullptr, float* gamma = nullptr, int C = 0, long long k_stride = 0,
-                            long long v_stride = 0, const void* v_first = nullptr, const void* mix = nullptr) {
+                            long long v_stride = 0, const void* v_first = nullptr, const void* mix = nullptr,
+                            long long q_stride = 0, long long g_stride = 0) {
     if (!state || !q || !k || !v || !gate_raw || !log_dt_scale || !rope_freqs || !y)
         return CDSSM_ERR_BAD_ARG;
     if (corr && (!carry || !gamma || C <= 0 || (((uintptr_t)corr | (uintptr_t)carry) & 15))) return CDSSM_ERR_BAD_ARG;
@@ -1044,12 +1046,15 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
     a.k_stride = k_stride ? k_stride : (long long)H * D;
     a.v_stride = v_stride ? v_stride : (long long)H * N;
     a.v_first = v_first; a.mix = mix;
+    a.q_stride = q_stride ? q_stride : (long long)H * D;
+    a.g_stride = g_stride ? g_stride : (long long)(N + 5) * H;
     {
         const long long es = dtype == CDSSM_F32 ? 4 : 2;
-        if ((a.k_stride * es) & 15) return CDSSM_ERR_BAD_ARG;                 // 16-byte row loads of k
+        if (((a.k_stride | a.q_stride) * es) & 15) return CDSSM_ERR_BAD_ARG;   // 16-byte row loads of k and q
+        if (a.q_stride < (long long)H * D || a.g_stride < (long long)(N + 5) * H) return CDSSM_ERR_BAD_ARG;
         if (a.k_stride < (long long)H * D || a.v_stride < (long long)H * N) return CDSSM_ERR_BAD_ARG;
         if ((v_first != nullptr) != (mix != nullptr)) return CDSSM_ERR_BAD_ARG;
-        if (corr && (v_first || k_stride || v_stride)) return CDSSM_ERR_UNSUPPORTED;
+        if (corr && (v_first || k_stride || v_stride || q_stride || g_stride)) return CDSSM_ERR_UNSUPPORTED;
     }
     a.log_dt_scale = log_dt_scale; a.rope_freqs = rope_freqs; a.y = y;
     a.dc = DynConsts{gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps};
@@ -1198,17 +1203,19 @@ extern "C" int cdssm_b200_decode_step_at(float* state, const void* q, const void
                             dtype, stream);
 }
 
-extern "C" int cdssm_b200_decode_step_strided(float* state, const void* q, const void* k, int64_t k_row_stride,
-                                              const void* v, int64_t v_row_stride, const void* v_first,
-                                              const void* mix, const void* gate_raw, const float* log_dt_scale,
+extern "C" int cdssm_b200_decode_step_strided(float* state, const void* q, int64_t q_row_stride, const void* k,
+                                              int64_t k_row_stride, const void* v, int64_t v_row_stride,
+                                              const void* v_first, const void* mix, const void* gate_raw,
+                                              int64_t gate_row_stride, const float* log_dt_scale,
                                               const float* rope_freqs, void* y, float gating_c, float omega_thresh,
                                               float adt_delta, float adt_smoothness, float adt_eps,
                                               float shortcut_scale, int B, int H, int D, int N, int pos,
                                               const int* pos_dev, int dtype, void* stream) {
-    if (k_row_stride <= 0 || v_row_stride <= 0) return CDSSM_ERR_BAD_ARG;
+    if (k_row_stride <= 0 || v_row_stride <= 0 || q_row_stride <= 0 || gate_row_stride <= 0) return CDSSM_ERR_BAD_ARG;
     return decode_step_impl(state, q, k, v, gate_raw, log_dt_scale, rope_freqs, y, gating_c, omega_thresh,
                             adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, pos, pos_dev, dtype,
-                            stream, nullptr, nullptr, nullptr, 0, k_row_stride, v_row_stride, v_first, mix);
+                            stream, nullptr, nullptr, nullptr, 0, k_row_stride, v_row_stride, v_first, mix, q_row_stride,
+                            gate_row_stride);
 }
 
 extern "C" int cdssm_b200_decode_step_reference(float* local_state, float* correction, float* carry, float* chunk_decay,

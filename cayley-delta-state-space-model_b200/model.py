@@ -108,7 +108,16 @@ class CdssmBlockParams:
         self.D = to(torch.zeros(di))
         self.v_residual_gate = torch.zeros(H, device=device, dtype=torch.float32)
         self.shortcut_scale = 0.0
+        self.merge_q_and_gate_projections()
 
+
+    def merge_q_and_gate_projections(self):
+        """Q_proj and gate_proj read the same conv output: keep their weights as the two row blocks of ONE matrix,
+        so that a decode step runs one product for both (the separate weights stay available as views)."""
+        di = self.w_q.shape[0]
+        self.w_qg = torch.cat([self.w_q, self.w_gate]).contiguous()
+        self.b_qg = torch.cat([torch.zeros(di, device=self.b_gate.device, dtype=self.b_gate.dtype), self.b_gate])
+        self.w_q, self.w_gate = self.w_qg[:di], self.w_qg[di:]
 
     def residual_mix(self, dtype):
         """sigmoid(v_residual_gate) in the activation dtype (block.py:167-171), computed once per value of the
@@ -135,6 +144,7 @@ class CdssmBlockParams:
         self.D = to("D")
         self.v_residual_gate = f32("v_residual_gate")
         self.shortcut_scale = float(sd[prefix + "shortcut_scale"].float().item())
+        self.merge_q_and_gate_projections()
 
 
 class CdssmLM:
@@ -202,8 +212,12 @@ class CdssmLM:
                 cache["conv"] = hist
         else:                                   # decode: one output from the cached history, shifted in place
             x_conv = ops.conv1d_silu_step(x_gate[:, 0], cache["conv"], p.conv_w, p.conv_b).unsqueeze(1)
-        gates = F.linear(x_conv, p.w_gate, p.b_gate)
-        Q = F.linear(x_conv, p.w_q).reshape(B, L, H, cfg.head_dim)
+        if decoding:                            # one product for Q and the gates; the step kernel reads the slices
+            qg = F.linear(x_conv, p.w_qg, p.b_qg)
+            Q, gates = qg[..., :di].unflatten(-1, (H, cfg.head_dim)), qg[..., di:]
+        else:
+            gates = F.linear(x_conv, p.w_gate, p.b_gate)
+            Q = F.linear(x_conv, p.w_q).reshape(B, L, H, cfg.head_dim)
         if decoding:
             y = ops.decode_step(cache["state"], Q[:, 0], K[:, 0], V[:, 0], gates[:, 0], p.log_dt_scale,
                                 p.rope_freqs, *cfg.dyn_consts, H, N, pos0, shortcut_scale=p.shortcut_scale,

@@ -412,20 +412,25 @@ def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor
     for every new token); the update is one iteration of intra_chunk_scan.cu:117-167 with the
     gates of dynamics_fused.cu:64-139 at position ``pos``.
     """
-    q = _prep(q, name="q")
+    if not q.is_cuda:
+        raise CdssmError("q must be a CUDA tensor (no CPU fallback exists)")
     B, H, D = q.shape
     N = int(state_dim)
+    dt = q.dtype
 
-    def rows(t, inner, name):
-        """(B,H,inner) with contiguous rows; the batch stride may be larger (a slice of a projection)."""
-        if t.is_cuda and t.dtype == q.dtype and tuple(t.shape) == (B, H, inner) and t.stride(2) == 1 and \
-                t.stride(1) == inner and t.stride(0) >= H * inner and \
-                (t.stride(0) * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0:
-            return t
-        return _prep(t, dtype=q.dtype, name=name)
+    def rows(t, shape, name):
+        """Rows dense inside; only the batch stride may be larger (a column slice of a projection)."""
+        ok = t.is_cuda and t.dtype == dt and tuple(t.shape) == tuple(shape)
+        inner = 1
+        for i in range(len(shape) - 1, 0, -1):
+            ok = ok and t.stride(i) == inner
+            inner *= shape[i]
+        ok = ok and t.stride(0) >= inner and (t.stride(0) * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
+        return t if ok else _prep(t, dtype=dt, name=name)
 
-    k, v = rows(k, D, "k"), rows(v, N, "v")
-    g = _prep(gate_raw, dtype=q.dtype, name="gate_raw")
+    q = rows(q, (B, H, D), "q")
+    k, v = rows(k, (B, H, D), "k"), rows(v, (B, H, N), "v")
+    g = rows(gate_raw, (B, (N + 5) * H), "gate_raw")
     if not state.is_cuda or state.dtype != torch.float32 or not state.is_contiguous():
         raise CdssmError("state must be a contiguous float32 CUDA tensor (B,H,N,D)")
     if H != int(n_heads) or tuple(state.shape) != (B, H, N, D) or tuple(k.shape) != (B, H, D) or \
@@ -445,7 +450,8 @@ def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor
         raise CdssmError("a tensor position must be an int32 CUDA tensor")   # device memory: graph-replayable
     with torch.cuda.device(q.device):
         check(_lib.lib().cdssm_b200_decode_step_strided(
-            _p(state), _p(q), _p(k), k.stride(0), _p(v), v.stride(0), _p(v_first), _p(mix), _p(g), _p(lds), _p(rf),
+            _p(state), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(v_first), _p(mix), _p(g),
+            g.stride(0), _p(lds), _p(rf),
             _p(y), gating_c, omega_thresh, adt_delta, adt_smoothness, adt_eps, shortcut_scale, B, H, D, N, pos_i,
             _p(pos_dev), _dtype_code(q), _stream()), "decode_step")
     return y

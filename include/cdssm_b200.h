@@ -346,14 +346,15 @@ CDSSM_API int cdssm_b200_decode_step_at(float* state, const void* q, const void*
                                         float adt_eps, float shortcut_scale, int B, int H, int D, int N,
                                         const int* pos_dev, int dtype, void* stream);
 
-/* cdssm_b200_decode_step for k and v that are column slices of a wider per-token projection (k_row_stride /
- * v_row_stride elements between batch rows; k rows 16-byte aligned) and, if v_first and mix are not NULL, with the
+/* cdssm_b200_decode_step for q, k, v and gate_raw that are column slices of wider per-token projections (*_row_stride
+ * elements between batch rows; q and k rows 16-byte aligned) and, if v_first and mix are not NULL, with the
  * value residual of cdssm/models/block.py:167-171 applied on the fly: v <- lerp(v_first, v, mix[head]) rounded to
  * the storage type (v_first (B,H,N) contiguous, mix (H) in the storage type = sigmoid(v_residual_gate)).  Saves
  * the copy of k and the lerp kernel of a decode step.  pos_dev as in cdssm_b200_decode_step_at (or NULL). */
-CDSSM_API int cdssm_b200_decode_step_strided(float* state, const void* q, const void* k, int64_t k_row_stride,
-                                             const void* v, int64_t v_row_stride, const void* v_first,
-                                             const void* mix, const void* gate_raw, const float* log_dt_scale,
+CDSSM_API int cdssm_b200_decode_step_strided(float* state, const void* q, int64_t q_row_stride, const void* k,
+                                             int64_t k_row_stride, const void* v, int64_t v_row_stride,
+                                             const void* v_first, const void* mix, const void* gate_raw,
+                                             int64_t gate_row_stride, const float* log_dt_scale,
                                              const float* rope_freqs, void* y, float gating_c, float omega_thresh,
                                              float adt_delta, float adt_smoothness, float adt_eps,
                                              float shortcut_scale, int B, int H, int D, int N, int pos,
