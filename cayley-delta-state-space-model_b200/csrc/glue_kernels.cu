@@ -10,28 +10,6 @@
 
 namespace cdssm {
 
-template <typename T> struct Vec8;   // eight consecutive elements
-template <> struct Vec8<__nv_bfloat16> {
-    static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float* f) {
-        unpack8(*reinterpret_cast<const uint4*>(p), f);
-    }
-    static __device__ __forceinline__ void st(__nv_bfloat16* p, const float* f) {
-        uint4 r;
-        r.x = pack2(f[0], f[1]); r.y = pack2(f[2], f[3]); r.z = pack2(f[4], f[5]); r.w = pack2(f[6], f[7]);
-        *reinterpret_cast<uint4*>(p) = r;
-    }
-};
-template <> struct Vec8<float> {
-    static __device__ __forceinline__ void ld(const float* p, float* f) {
-        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-    }
-    static __device__ __forceinline__ void st(float* p, const float* f) {
-        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-        *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
-    }
-};
-
 // ---------------------------------------------------------------- RMSNorm
 // One warp per row: out = rnd(rnd(x * rsqrt(mean x^2 + eps)) * w)   (modules.py:50-53)
 template <typename T>
@@ -133,21 +111,30 @@ groupnorm_partial_kernel(const T* __restrict__ y, float* __restrict__ partial, i
     }
 }
 
-__global__ void groupnorm_finalize_kernel(const float* __restrict__ partial, float* __restrict__ stats, int total,
-                                          int L, int cg, int groups, int tiles, float eps) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // (batch row, group)
+__global__ void __launch_bounds__(128)
+groupnorm_finalize_kernel(const float* __restrict__ partial, float* __restrict__ stats, int total, int L, int cg,
+                          int groups, int tiles, float eps) {
+    const int i = blockIdx.x * 4 + (threadIdx.x >> 5);     // (batch row, group): one warp each
     if (i >= total) return;
+    const int lane = threadIdx.x & 31;
     const int b = i / groups, grp = i % groups;
     double s = 0.0, q = 0.0;
-    for (int t = 0; t < tiles; t++) {
+    for (int t = lane; t < tiles; t += 32) {               // lane-strided, then a fixed shuffle tree: deterministic
         const float* p = partial + (((long long)b * tiles + t) * groups + grp) * 2;
         s += (double)p[0];
         q += (double)p[1];
     }
-    const double n = (double)L * cg, mean = s / n;
-    const double var = fmax(q / n - mean * mean, 0.0);
-    stats[2 * i] = (float)mean;
-    stats[2 * i + 1] = (float)(1.0 / sqrt(var + (double)eps));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+        q += __shfl_xor_sync(0xffffffffu, q, o);
+    }
+    if (lane == 0) {
+        const double n = (double)L * cg, mean = s / n;
+        const double var = fmax(q / n - mean * mean, 0.0);
+        stats[2 * i] = (float)mean;
+        stats[2 * i + 1] = (float)(1.0 / sqrt(var + (double)eps));
+    }
 }
 
 // ---------------------------------------------------------------- GroupNorm + gate + skip
@@ -193,10 +180,49 @@ groupnorm_gate_fwd_kernel(const T* __restrict__ y, const float* __restrict__ sta
 #pragma unroll
     for (int e = 0; e < 8; e++) {
         const float n = IO<T>::rnd((f[e] - mean) * rstd * gw[e] + gb[e]);
-        const float g = IO<T>::rnd(siluf_<false>(zz[e]));
+        const float g = IO<T>::rnd(siluf_<IO<T>::kBf16>(zz[e]));
         f[e] = IO<T>::rnd(n * g) + IO<T>::rnd(sk[e] * xc[e]);
     }
     Vec8<T>::st(out + row * di + c, f);
+}
+
+// The same with statistics given, kRows tokens per block: the per-channel parameters are loaded once and the
+// loads of all rows are in flight together.
+template <typename T, int kRows>
+__global__ void __launch_bounds__(1024)
+groupnorm_gate_rows_kernel(const T* __restrict__ y, const float* __restrict__ stats, const T* __restrict__ gn_w,
+                           const T* __restrict__ gn_b, const T* __restrict__ z, long long z_row_stride,
+                           const T* __restrict__ skip, const T* __restrict__ x_conv, T* __restrict__ out,
+                           long long rows, int L, int di, int groups) {
+    const long long r0 = (long long)blockIdx.x * kRows;
+    const int c = threadIdx.x * 8;
+    const int grp = threadIdx.x / ((di / groups) / 8);
+    float f[kRows][8], zz[kRows][8], xc[kRows][8], mean[kRows], rstd[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; r++) {
+        const long long row = r0 + r < rows ? r0 + r : rows - 1;
+        Vec8<T>::ld(y + row * di + c, f[r]);
+        Vec8<T>::ld(z + row * z_row_stride + c, zz[r]);
+        Vec8<T>::ld(x_conv + row * di + c, xc[r]);
+        const long long b = row / L;
+        mean[r] = stats[2 * (b * groups + grp)];
+        rstd[r] = stats[2 * (b * groups + grp) + 1];
+    }
+    float gw[8], gb[8], sk[8];
+    Vec8<T>::ld(gn_w + c, gw);
+    Vec8<T>::ld(gn_b + c, gb);
+    Vec8<T>::ld(skip + c, sk);
+#pragma unroll
+    for (int r = 0; r < kRows; r++) {
+        if (r0 + r >= rows) break;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float n = IO<T>::rnd((f[r][e] - mean[r]) * rstd[r] * gw[e] + gb[e]);
+            const float g = IO<T>::rnd(siluf_<IO<T>::kBf16>(zz[r][e]));
+            f[r][e] = IO<T>::rnd(n * g) + IO<T>::rnd(sk[e] * xc[r][e]);
+        }
+        Vec8<T>::st(out + (r0 + r) * di + c, f[r]);
+    }
 }
 
 // ---------------------------------------------------------------- one-token conv + SiLU on a cached history
@@ -303,7 +329,7 @@ extern "C" int cdssm_b200_groupnorm_stats(const void* y, float* stats, int B, in
                               (const T*)y, partial, L, di, groups, tiles)));
     if (int rc = check_launch()) return rc;
     const int total = B * groups;
-    groupnorm_finalize_kernel<<<(unsigned)((total + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+    groupnorm_finalize_kernel<<<(unsigned)((total + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
         partial, stats, total, L, di / groups, groups, tiles, eps);
     return check_launch();
 }
@@ -321,6 +347,14 @@ extern "C" int cdssm_b200_groupnorm_gate_fwd(const void* y, const float* stats, 
     const long long rows = (long long)B * L;
     if (rows == 0) return CDSSM_OK;
     if (rows > 0x7fffffffLL) return CDSSM_ERR_UNSUPPORTED;
+    if (stats != nullptr && rows >= 4096) {
+        constexpr int kRows = 4;
+        DISPATCH_DTYPE(dtype, (groupnorm_gate_rows_kernel<T, kRows><<<(unsigned)((rows + kRows - 1) / kRows), di / 8, 0,
+                                                                      (cudaStream_t)stream>>>(
+                                  (const T*)y, stats, (const T*)gn_weight, (const T*)gn_bias, (const T*)z, z_row_stride,
+                                  (const T*)skip, (const T*)x_conv, (T*)out, rows, L, di, groups)));
+        return check_launch();
+    }
     DISPATCH_DTYPE(dtype, (groupnorm_gate_fwd_kernel<T><<<(unsigned)rows, di / 8, 0, (cudaStream_t)stream>>>(
                               (const T*)y, stats, (const T*)gn_weight, (const T*)gn_bias, (const T*)z, z_row_stride,
                               (const T*)skip, (const T*)x_conv, (T*)out, L, di, groups, eps)));
