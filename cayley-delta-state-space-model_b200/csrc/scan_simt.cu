@@ -1050,7 +1050,8 @@ static int decode_step_impl(float* state, const void* q, const void* k, const vo
     a.g_stride = g_stride ? g_stride : (long long)(N + 5) * H;
     {
         const long long es = dtype == CDSSM_F32 ? 4 : 2;
-        if (((a.k_stride | a.q_stride) * es) & 15) return CDSSM_ERR_BAD_ARG;   // 16-byte row loads of k and q
+        const bool vec_rows = D == 64 || D == 128;                             // 16-byte row loads of k and q
+        if (vec_rows && (((a.k_stride | a.q_stride) * es) & 15)) return CDSSM_ERR_BAD_ARG;
         if (a.q_stride < (long long)H * D || a.g_stride < (long long)(N + 5) * H) return CDSSM_ERR_BAD_ARG;
         if (a.k_stride < (long long)H * D || a.v_stride < (long long)H * N) return CDSSM_ERR_BAD_ARG;
         if ((v_first != nullptr) != (mix != nullptr)) return CDSSM_ERR_BAD_ARG;

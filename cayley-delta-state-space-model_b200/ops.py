@@ -426,7 +426,7 @@ def decode_step(state: Tensor, q: Tensor, k: Tensor, v: Tensor, gate_raw: Tensor
             ok = ok and t.stride(i) == inner
             inner *= shape[i]
         ok = ok and t.stride(0) >= inner and (t.stride(0) * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
-        return t if ok else _prep(t, dtype=dt, name=name)
+        return t if ok else _prep(t, dtype=dt, name=name)       # anything else: a dense copy (as before)
 
     q = rows(q, (B, H, D), "q")
     k, v = rows(k, (B, H, D), "k"), rows(v, (B, H, N), "v")
