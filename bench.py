@@ -340,9 +340,16 @@ def lm_arm(args, w, rank, world, local_rank):
         else:
             dids = ids.to(dev)
             caches = []
+            lm.prefill(dids[:min(Bl, 16), :256])    # warm-up of the library handles before the prefill is timed
+            torch.cuda.synchronize()
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record()
             for b0 in range(0, Bl, 16):             # prefill in slices: activations of 16 x 4096 tokens
                 logits, c = lm.prefill(dids[b0:b0 + 16])
                 caches.append((logits[:, -1].argmax(-1), c))
+            p1.record()
+            torch.cuda.synchronize()
+            prefill_ms = p0.elapsed_time(p1)
             tok = torch.cat([c[0] for c in caches])
             cache = {"pos": w["L"], "layers": [
                 {k: torch.cat([c[1]["layers"][i][k] for c in caches]) for k in ("state", "conv")}
@@ -385,6 +392,9 @@ def lm_arm(args, w, rank, world, local_rank):
         if not decode:
             line["scan_share"] = scan_share
         if decode:
+            line["prefill"] = {"ms": prefill_ms, "tokens_per_s": Bl * w["L"] / (prefill_ms / 1e3) * world,
+                               "what": f"the {w['L']}-token prefill that fills the decode cache, {Bl} sequences in slices "
+                                       "of 16, issued eagerly, once (rank 0's time)"}
             per_bh = 2 * N * D * 4 + 2 * D * 2 + (3 * N + 5) * 2
             line["decode_state_bytes_per_step"] = cfg.n_layers * w["B"] * H * per_bh / world
         print(json.dumps(line))
