@@ -12,7 +12,7 @@ def _tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,d", [(5, 128), (300, 768), (33, 2048)])
+@pytest.mark.parametrize("rows,d", [(5, 128), (300, 768), (33, 2048), (2500, 256), (7, 4096)])   # both kernels
 def test_rms_norm(ops, dtype, rows, d):
     g = torch.Generator(device="cuda").manual_seed(rows + d)
     x = (torch.randn(rows, d, generator=g, device="cuda") * 3).to(dtype)
@@ -28,7 +28,8 @@ def test_rms_norm(ops, dtype, rows, d):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("per_token", [False, True])
-@pytest.mark.parametrize("B,L,di", [(2, 37, 256), (1, 200, 1536), (3, 1, 4096)])
+@pytest.mark.parametrize("B,L,di", [(2, 37, 256), (1, 200, 1536), (3, 1, 4096),
+                                    (2, 2101, 256), (3, 1400, 768)])   # >= 4096 rows: the four-rows-per-block kernel
 def test_groupnorm_gate(ops, dtype, per_token, B, L, di):
     G = 32
     g = torch.Generator(device="cuda").manual_seed(L + di)
@@ -50,8 +51,9 @@ def test_groupnorm_gate(ops, dtype, per_token, B, L, di):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_conv_step_equals_full_conv(ops, dtype):
-    B, L, Dm = 3, 9, 256
+@pytest.mark.parametrize("Dm", [256, 52])                      # 16-byte vectors / the element-wise kernel
+def test_conv_step_equals_full_conv(ops, dtype, Dm):
+    B, L = 3, 9
     g = torch.Generator(device="cuda").manual_seed(3)
     x = torch.randn(B, L, Dm, generator=g, device="cuda").to(dtype)
     w = (torch.randn(Dm, 1, 4, generator=g, device="cuda") / 2).to(dtype)
