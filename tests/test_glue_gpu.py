@@ -29,7 +29,8 @@ def test_rms_norm(ops, dtype, rows, d):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("per_token", [False, True])
 @pytest.mark.parametrize("B,L,di", [(2, 37, 256), (1, 200, 1536), (3, 1, 4096),
-                                    (2, 2101, 256), (3, 1400, 768)])   # >= 4096 rows: the four-rows-per-block kernel
+                                    (2, 2101, 256), (3, 1400, 768),     # >= 4096 rows: the four-rows-per-block kernel
+                                    (1, 20000, 256)])                   # more positions than 512 tiles of 32
 def test_groupnorm_gate(ops, dtype, per_token, B, L, di):
     G = 32
     g = torch.Generator(device="cuda").manual_seed(L + di)
